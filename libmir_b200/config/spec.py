@@ -188,6 +188,14 @@ class SoftmaxAttentionSpec(PartSpec):
     value_head_dim: Optional[int] = None     # width of a value head where it differs from head_dim
     keep_first: int = 0                      # with a window: the first tokens every later query still sees
     names: tuple = ()                        # (local name, stored name) pairs for checkpoints with names of their own
+    # sinks: the softmax's denominator also holds exp(s_h) of one stored number per query head (tensor `sink`), which
+    # has no key and no value and is not scaled.  gate: the concatenated heads are multiplied by the sigmoid of a
+    # projection (tensor `g`) of the mixer's input before the output projection.  own_kv False: the mixer has no key
+    # and value tensors; it attends with its own queries over the cache of the schedule entry that its entry names
+    # (ScheduleEntry.cache_of), whose head counts, widths and rotation must equal its own.
+    sinks: bool = False
+    gate: bool = False
+    own_kv: bool = True
     kind: str = field(init=False, default="softmax_attention")
 
     @property
@@ -204,8 +212,8 @@ class SwiGluSpec(PartSpec):
 
 @dataclass(frozen=True)
 class GeluMlpSpec(PartSpec):
-    """down(gelu(up(x))): a dense feed-forward without a gate.  `activation`: "gelu_tanh" (the tanh form) or
-    "gelu_erf" (the exact form)."""
+    """down(act(up(x))): a dense feed-forward without a gate.  `activation`: "gelu_tanh" (the tanh form), "gelu_erf"
+    (the exact form) or "relu2" (the square of relu)."""
 
     hidden_size: int = 0
     intermediate_size: int = 0
@@ -271,6 +279,23 @@ class RoutedExpertsSpec(PartSpec):
 
 
 @dataclass(frozen=True)
+class RetentionSpec(PartSpec):
+    """Linear attention with one fixed decay per head and no softmax (parts/retention.py): per head a matrix state
+    S <- decay_h S + k v^T, read out as S^T q, with k scaled by key_dim^-1/2 after the rotation; the read-out of each
+    head is divided by its root mean square and multiplied by silu of a projection of the mixer's input.  `decays`
+    holds one number per head."""
+
+    hidden_size: int = 0
+    heads: int = 0
+    key_dim: int = 0
+    value_dim: int = 0
+    decays: tuple = ()
+    norm_eps: float = 1e-5
+    position: Optional[PartSpec] = None
+    kind: str = field(init=False, default="retention")
+
+
+@dataclass(frozen=True)
 class GatedDeltaRuleSpec(PartSpec):
     """The gated delta rule (parts/delta_rule.py).  `decay`: "head" one decay per head from a full projection `a`,
     "channel" one per head and key channel from a low-rank pair `a1`, `a2` of rank `decay_rank`.  `gate`: "silu" of
@@ -321,9 +346,10 @@ class LayerSpec:
 
     `prefix` is the checkpoint prefix of the layer; `names` maps each slot of the
     arrangement to the sub-prefix of its tensors, so names are data of the architecture.
-    Arrangements: "pre_norm" (a norm before each of the two branches, one after the other) and "parallel" (both
+    Arrangements: "pre_norm" (a norm before each of the two branches, one after the other), "parallel" (both
     branches read the same residual and their results are added to it together: through one norm, `mixer_norm`, if
-    `feed_forward_norm` is None, else each through a norm of its own).
+    `feed_forward_norm` is None, else each through a norm of its own) and "output_norm" (each branch reads the
+    residual itself and its RESULT goes through the norm: x += residual_scale * norm(branch(x)), one after the other).
     """
 
     prefix: str
@@ -333,6 +359,7 @@ class LayerSpec:
     feed_forward_norm: Optional[PartSpec]
     names: Mapping[str, str]
     arrangement: str = "pre_norm"
+    residual_scale: float = 1.0           # what a branch's (normed) result is multiplied by ("output_norm" only)
 
 
 @dataclass(frozen=True)
@@ -366,6 +393,8 @@ class EmbeddingSpec:
     hidden_size: int
     multiplier: float = 1.0
     pairs: Optional[TokenPairsSpec] = None
+    norm: Optional[PartSpec] = None       # a norm applied to the embedded rows before the first layer,
+    norm_name: str = ""                   # stored under this name
 
 
 @dataclass(frozen=True)

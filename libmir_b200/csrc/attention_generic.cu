@@ -16,6 +16,9 @@
 // than keys (value_dim).  A query walks over the kept keys first, then over its window.  Consecutive value rows
 // lie value_row_width elements apart: value_dim in a cache of their own, head_dim where the values are the first
 // value_dim elements of the keys themselves (a latent that is read both ways; v_pages is then k_pages).
+// sinks (one 32-bit number per query head, or none): exp(sink - max) is added to the softmax's denominator once; it
+// has no key and no value and is not scaled.  gate (rows of the activations' type with a stride of their own, or
+// none): the head's result is multiplied by the sigmoid of its gate elements before it is stored.
 #include <cfloat>
 #include "common.cuh"
 
@@ -29,7 +32,8 @@ __global__ void paged_attention_generic_kernel(
     const T* __restrict__ q, size_t q_token_stride, T* __restrict__ out, const T* __restrict__ k_pages,
     const T* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
     const int* __restrict__ row_of_token, const int* __restrict__ positions, int page_size, int heads, int kv_heads,
-    int head_dim, int value_dim, int value_row_width, float scale, int window, int keep_first) {
+    int head_dim, int value_dim, int value_row_width, float scale, int window, int keep_first,
+    const float* __restrict__ sinks, const T* __restrict__ gate, size_t gate_stride) {
   __shared__ float q_shared[kWarpsPerBlock][kMaxHeadDim];
   const int lane = threadIdx.x;
   const int warp = threadIdx.y;
@@ -101,12 +105,25 @@ __global__ void paged_attention_generic_kernel(
     running_max = next_max;
   }
 
+  if (sinks != nullptr && position >= 0) {
+    const float sink = sinks[head];
+    const float next_max = fmaxf(running_max, sink);
+    const float correction = expf(running_max - next_max);
+    denominator = denominator * correction + expf(sink - next_max);
+#pragma unroll
+    for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] *= correction;
+  }
   T* out_row = out + ((size_t)token * heads + head) * value_dim;
+  const T* gate_row = gate != nullptr ? gate + (size_t)token * gate_stride + (size_t)head * value_dim : nullptr;
   const float inverse = denominator > 0.0f ? 1.0f / denominator : 0.0f;   // a padded row has no keys
 #pragma unroll
   for (int i = 0; i < kMaxHeadDim / 32; ++i) {
     const int d = lane + 32 * i;
-    if (d < value_dim) out_row[d] = from_float<T>(acc[i] * inverse);
+    if (d < value_dim) {
+      float result = acc[i] * inverse;
+      if (gate_row != nullptr) result *= 1.0f / (1.0f + expf(-to_float(gate_row[d])));
+      out_row[d] = from_float<T>(result);
+    }
   }
 }
 
@@ -116,6 +133,7 @@ MIR_EXPORT int mir_paged_attention_generic(int bf16, const void* q, long long q_
                                            int table_width, const int* row_of_token, const int* positions, int tokens,
                                            int page_size, int heads, int kv_heads, int head_dim, int value_dim,
                                            float scale, int window, int keep_first, int value_row_width,
+                                           const float* sinks, const void* gate, long long gate_stride,
                                            cudaStream_t stream) {
   if (tokens == 0) return MIR_OK;
   if (tokens < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || page_size <= 0 || table_width <= 0 ||
@@ -139,11 +157,12 @@ MIR_EXPORT int mir_paged_attention_generic(int bf16, const void* q, long long q_
     paged_attention_generic_kernel<<<grid, block, 0, stream>>>(
         (const __nv_bfloat16*)q, (size_t)q_token_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pages,
         (const __nv_bfloat16*)v_pages, block_table, table_width, row_of_token, positions, page_size, heads, kv_heads,
-        head_dim, value_dim, value_row_width, scale, window, keep_first);
+        head_dim, value_dim, value_row_width, scale, window, keep_first, sinks, (const __nv_bfloat16*)gate,
+        (size_t)gate_stride);
   else
     paged_attention_generic_kernel<<<grid, block, 0, stream>>>(
         (const float*)q, (size_t)q_token_stride, (float*)out, (const float*)k_pages, (const float*)v_pages,
         block_table, table_width, row_of_token, positions, page_size, heads, kv_heads, head_dim, value_dim,
-        value_row_width, scale, window, keep_first);
+        value_row_width, scale, window, keep_first, sinks, (const float*)gate, (size_t)gate_stride);
   return mir_check_launch("paged_attention_generic");
 }

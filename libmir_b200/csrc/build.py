@@ -33,7 +33,8 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-Xc
 LIBRARIES = {
     "core": {
         "sources": ["runtime.cu", "elementwise.cu", "qk_rope_store.cu", "attention_generic.cu", "gemm_f32.cu",
-                    "sampling.cu", "executor.cu", "delta_rule.cu", "latent_attention.cu", "wkv.cu", "moe.cu"],
+                    "sampling.cu", "executor.cu", "delta_rule.cu", "latent_attention.cu", "wkv.cu", "moe.cu",
+                    "retention.cu"],
         "link": [],
         "defines": [],
     },

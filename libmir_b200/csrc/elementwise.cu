@@ -273,13 +273,16 @@ MIR_EXPORT int mir_embed_pairs(int bf16, const void* table, const void* pairs, c
                     (const float*)pairs, ids, previous, out, hidden, vocab, buckets, mul_previous, mul_current, scale);
 }
 
-// x <- act(x) in place: kind 1 the exact GELU 0.5 x (1 + erf(x / sqrt 2)), kind 2 tanh; computed in 32-bit.
+// x <- act(x) in place: kind 1 the exact GELU 0.5 x (1 + erf(x / sqrt 2)), kind 2 tanh, kind 3 the square of relu;
+// computed in 32-bit.
 template <typename T>
 __global__ void activation_kernel(T* __restrict__ x, size_t total, int kind) {
   const size_t index = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (index >= total) return;
   const float z = to_float(x[index]);
-  x[index] = from_float<T>(kind == 1 ? 0.5f * z * (1.0f + erff(z * 0.70710678118654752f)) : tanhf(z));
+  const float positive = fmaxf(z, 0.0f);
+  x[index] = from_float<T>(kind == 1 ? 0.5f * z * (1.0f + erff(z * 0.70710678118654752f))
+                                     : (kind == 2 ? tanhf(z) : positive * positive));
 }
 
 // x <- cap * tanh(x / cap) on 32-bit logits.
@@ -371,10 +374,10 @@ MIR_EXPORT int mir_rms_norm(int bf16, const float* x, const float* weight, void*
 }
 
 MIR_EXPORT int mir_activation(int kind, int bf16, void* x, size_t total, cudaStream_t stream) {
-  if (kind != 1 && kind != 2) { mir_set_error("activation: unknown kind %d", kind); return MIR_BAD_ARGUMENT; }
+  if (kind < 1 || kind > 3) { mir_set_error("activation: unknown kind %d", kind); return MIR_BAD_ARGUMENT; }
   if (bf16) LAUNCH_1D(activation_kernel, total, (__nv_bfloat16*)x, total, kind);
   else LAUNCH_1D(activation_kernel, total, (float*)x, total, kind);
-  return mir_check_launch(kind == 1 ? "gelu_erf" : "tanh");
+  return mir_check_launch(kind == 1 ? "gelu_erf" : (kind == 2 ? "tanh" : "relu_squared"));
 }
 
 MIR_EXPORT int mir_softcap(float* x, size_t total, float cap, cudaStream_t stream) {

@@ -200,7 +200,8 @@ struct Run {
     return mir_paged_attention_generic(step.bf16, step.qkv, width, step.mixed, layer.k_pages, layer.v_pages,
                                        group.block_table, group.table_width, step.row_of_token, step.positions,
                                        step.tokens, layer.page_size, layer.heads, layer.kv_heads, layer.head_dim,
-                                       layer.head_dim, layer.scale, layer.window, 0, 0, step.stream);
+                                       layer.head_dim, layer.scale, layer.window, 0, 0, nullptr, nullptr, 0,
+                                       step.stream);
   }
 
   int feed_forward(const MirLayerDesc& layer, const MirNormDesc* upcoming) {
@@ -280,7 +281,7 @@ MIR_EXPORT int mir_run_layers(const MirLayerDesc* layers, int count, const MirSt
     MIR_TRY(mir_qk_rope_store(step->bf16, step->qkv, step->positions, group.slot_mapping, layer.inv_freq, layer.q_norm,
                               layer.k_norm, layer.k_pages, layer.v_pages, step->tokens, layer.heads, layer.kv_heads,
                               layer.head_dim, layer.head_dim, layer.rotary_dim, layer.qk_eps,
-                              layer.writes_cache ? 1 : 0, step->stream));
+                              layer.writes_cache ? 1 : 0, 0, 0, 0, step->stream));
     MIR_TRY(run.attend(layer));
     MIR_TRY(run.accumulate(step->mixed, layer.heads * layer.head_dim, layer.w_o, layer.b_o,
                            has_ff ? &layer.ff_norm : next_first));

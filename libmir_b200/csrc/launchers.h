@@ -14,13 +14,13 @@ int mir_add_bias(int bf16, float* x, const void* bias, int rows, int cols, cudaS
 int mir_qk_rope_store(int bf16, void* qkv, const int* positions, const int* slot_mapping, const float* inv_freq,
                       const float* q_norm, const float* k_norm, void* k_pages, void* v_pages, int tokens, int heads,
                       int kv_heads, int head_dim, int value_dim, int rotary_dim, float eps, int write_kv,
-                      cudaStream_t stream);
+                      int interleaved, long long row_stride, int queries_only, cudaStream_t stream);
 // attention_generic.cu
 int mir_paged_attention_generic(int bf16, const void* q, long long q_token_stride, void* out, const void* k_pages,
                                 const void* v_pages, const int* block_table, int table_width, const int* row_of_token,
                                 const int* positions, int tokens, int page_size, int heads, int kv_heads, int head_dim,
                                 int value_dim, float scale, int window, int keep_first, int value_row_width,
-                                cudaStream_t stream);
+                                const float* sinks, const void* gate, long long gate_stride, cudaStream_t stream);
 // gemm_f32.cu
 int mir_gemm_f32(const float* a, int lda, const float* w, int ldw, const float* bias, float* c, int ldc, int m, int n,
                  int k, float beta, cudaStream_t stream);

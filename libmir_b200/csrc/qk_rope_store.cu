@@ -13,6 +13,10 @@
 // write_kv: 0 only the queries are treated (a reader of another entry's cache), 1 keys and values go to their
 // pages, 2 keys are normed and rotated in place like the queries and nothing goes to the pages (a position
 // encoding of another kind works on them next; a second call with 1 and neither norm nor rotation then stores).
+// interleaved: dims 2i and 2i + 1 of the first rotary_dim dims form pair i, instead of dims i and i + rotary_dim / 2.
+// row_stride: elements from one token's row to the next where the row holds more than q, k and v (a gate's
+// projection behind them), 0 = packed.  queries_only: the rows hold the query heads alone (a mixer that attends over
+// another entry's keys and values).
 #include "common.cuh"
 #include "trace.cuh"
 
@@ -37,15 +41,16 @@ __global__ void qk_rope_store_kernel(T* __restrict__ qkv, const int* __restrict_
                                      const float* __restrict__ q_norm, const float* __restrict__ k_norm,
                                      T* __restrict__ k_pages, T* __restrict__ v_pages, int heads, int kv_heads,
                                      int head_dim, int value_dim, int rotary_dim, float eps, int write_kv,
-                                     int units_per_cta) {
+                                     int units_per_cta, int interleaved, long long row_stride, int queries_only) {
   extern __shared__ float angles[];                 // [half] cosines then [half] sines of this token
   grid_launch_dependents();
   grid_dependency_wait();
   const int token = blockIdx.x;
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-  const int units = heads + 2 * kv_heads;
-  const size_t row_width = (size_t)(heads + kv_heads) * head_dim + (size_t)kv_heads * value_dim;
+  const int units = queries_only ? heads : heads + 2 * kv_heads;
+  const size_t row_width = row_stride > 0 ? (size_t)row_stride
+                                          : (size_t)(heads + kv_heads) * head_dim + (size_t)kv_heads * value_dim;
   T* row = qkv + (size_t)token * row_width;
   const float position = (float)positions[token];
   const int slot = slot_mapping ? slot_mapping[token] : -1;
@@ -92,7 +97,27 @@ __global__ void qk_rope_store_kernel(T* __restrict__ qkv, const int* __restrict_
       inverse = rsqrtf(sum / (float)head_dim + eps);
     }
     T* dst = (is_query || key_in_place) ? src : k_pages + ((size_t)slot * kv_heads + (unit - heads)) * head_dim;
-    if (PAIRED) {
+    if (interleaved) {
+      // pair i is (2 i, 2 i + 1): a lane takes whole pairs, so the two layouts of the loop below do not apply
+      for (int pair = lane; pair < half; pair += 32) {
+        float first, second;
+        if (PAIRED) { const float2 v = load2(src + 2 * pair); first = v.x; second = v.y; }
+        else { first = to_float(src[2 * pair]); second = to_float(src[2 * pair + 1]); }
+        if (norm) {
+          first = first * inverse * norm[2 * pair];
+          second = second * inverse * norm[2 * pair + 1];
+        }
+        const float cosine = angles[pair], sine = angles[half + pair];
+        const float a = first * cosine - second * sine, b = second * cosine + first * sine;
+        if (PAIRED) store2(dst + 2 * pair, a, b);
+        else { dst[2 * pair] = from_float<T>(a); dst[2 * pair + 1] = from_float<T>(b); }
+      }
+      for (int d = rotary_dim + lane; d < head_dim; d += 32) {
+        float v = to_float(src[d]);
+        if (norm) v = v * inverse * norm[d];
+        dst[d] = from_float<T>(v);
+      }
+    } else if (PAIRED) {
       for (int pair = 2 * lane; pair < half; pair += 64) {
         float2 first = load2(src + pair), second = load2(src + pair + half);
         if (norm) {
@@ -243,30 +268,34 @@ int launch_rope_wide(__nv_bfloat16* qkv, const int* positions, const int* slot_m
 template <typename T>
 int launch_rope(T* qkv, const int* positions, const int* slot_mapping, const float* inv_freq, const float* q_norm,
                 const float* k_norm, T* k_pages, T* v_pages, int tokens, int heads, int kv_heads, int head_dim,
-                int value_dim, int rotary_dim, float eps, int write_kv, cudaStream_t stream) {
+                int value_dim, int rotary_dim, float eps, int write_kv, int interleaved, long long row_stride,
+                int queries_only, cudaStream_t stream) {
   // few tokens: 4 warps per CTA and enough CTAs per token to give every head a warp; many tokens: one CTA of 8
   // warps per token, so that the token's angles are computed once
-  const int units = heads + 2 * kv_heads;
+  const int units = queries_only ? heads : heads + 2 * kv_heads;
   const bool many = tokens >= 256;
   const int threads = many ? 256 : 128;
   const int units_per_cta = many ? units : 4;
   const dim3 grid(tokens, (units + units_per_cta - 1) / units_per_cta);
   const size_t smem = (size_t)rotary_dim * sizeof(float);
-  const bool paired = (head_dim % 2 == 0) && (value_dim % 2 == 0) && (rotary_dim % 4 == 0) && ((uintptr_t)qkv % (2 * sizeof(T)) == 0) &&
+  // (every head of a row, and every page row, then starts on an even element)
+  const bool paired = (head_dim % 2 == 0) && (value_dim % 2 == 0) && (rotary_dim % (interleaved ? 2 : 4) == 0) &&
+                      (row_stride % 2 == 0) && ((uintptr_t)qkv % (2 * sizeof(T)) == 0) &&
                       ((uintptr_t)k_pages % (2 * sizeof(T)) == 0);
   if (paired)
     return mir_launch("qk_rope_store", qk_rope_store_kernel<T, true>, grid, dim3(threads), smem, stream, 0, qkv, positions,
                       slot_mapping, inv_freq, q_norm, k_norm, k_pages, v_pages, heads, kv_heads, head_dim, value_dim,
-                      rotary_dim, eps, write_kv, units_per_cta);
+                      rotary_dim, eps, write_kv, units_per_cta, interleaved, row_stride, queries_only);
   return mir_launch("qk_rope_store", qk_rope_store_kernel<T, false>, grid, dim3(threads), smem, stream, 0, qkv, positions,
                     slot_mapping, inv_freq, q_norm, k_norm, k_pages, v_pages, heads, kv_heads, head_dim, value_dim,
-                    rotary_dim, eps, write_kv, units_per_cta);
+                    rotary_dim, eps, write_kv, units_per_cta, interleaved, row_stride, queries_only);
 }
 
 MIR_EXPORT int mir_qk_rope_store(int bf16, void* qkv, const int* positions, const int* slot_mapping,
                                  const float* inv_freq, const float* q_norm, const float* k_norm, void* k_pages,
                                  void* v_pages, int tokens, int heads, int kv_heads, int head_dim, int value_dim,
-                                 int rotary_dim, float eps, int write_kv, cudaStream_t stream) {
+                                 int rotary_dim, float eps, int write_kv, int interleaved, long long row_stride,
+                                 int queries_only, cudaStream_t stream) {
   if (tokens == 0) return MIR_OK;
   if (tokens < 0 || heads <= 0 || kv_heads <= 0 || head_dim <= 0 || value_dim <= 0 || rotary_dim < 0 || rotary_dim > head_dim ||
       (rotary_dim & 1)) {
@@ -275,8 +304,16 @@ MIR_EXPORT int mir_qk_rope_store(int bf16, void* qkv, const int* positions, cons
     return MIR_BAD_ARGUMENT;
   }
   if (rotary_dim > 8192) { mir_set_error("qk_rope_store: rotary_dim %d is too large", rotary_dim); return MIR_BAD_ARGUMENT; }
-  if (bf16 && rotary_dim == head_dim && value_dim == head_dim && head_dim % 16 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_pages & 15) == 0 &&
-      ((uintptr_t)v_pages & 15) == 0) {
+  const long long packed_width = (long long)(heads + kv_heads) * head_dim + (long long)kv_heads * value_dim;
+  if (row_stride < 0 || (row_stride > 0 && row_stride < (queries_only ? (long long)heads * head_dim : packed_width)) ||
+      (queries_only && (write_kv != 0 || row_stride == 0))) {
+    mir_set_error("qk_rope_store: a row stride of %lld does not hold the row, or rows of queries alone were asked to "
+                  "write keys", row_stride);
+    return MIR_BAD_ARGUMENT;
+  }
+  if (row_stride == packed_width && !queries_only) row_stride = 0;
+  if (bf16 && !interleaved && row_stride == 0 && rotary_dim == head_dim && value_dim == head_dim && head_dim % 16 == 0 &&
+      ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0) {
     __nv_bfloat16* q = (__nv_bfloat16*)qkv;
     __nv_bfloat16* kp = (__nv_bfloat16*)k_pages;
     __nv_bfloat16* vp = (__nv_bfloat16*)v_pages;
@@ -292,7 +329,8 @@ MIR_EXPORT int mir_qk_rope_store(int bf16, void* qkv, const int* positions, cons
   if (bf16)
     return launch_rope((__nv_bfloat16*)qkv, positions, slot_mapping, inv_freq, q_norm, k_norm, (__nv_bfloat16*)k_pages,
                        (__nv_bfloat16*)v_pages, tokens, heads, kv_heads, head_dim, value_dim, rotary_dim, eps, write_kv,
-                       stream);
+                       interleaved, row_stride, queries_only, stream);
   return launch_rope((float*)qkv, positions, slot_mapping, inv_freq, q_norm, k_norm, (float*)k_pages, (float*)v_pages,
-                     tokens, heads, kv_heads, head_dim, value_dim, rotary_dim, eps, write_kv, stream);
+                     tokens, heads, kv_heads, head_dim, value_dim, rotary_dim, eps, write_kv, interleaved, row_stride,
+                     queries_only, stream);
 }

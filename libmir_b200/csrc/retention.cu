@@ -1,0 +1,241 @@
+// The recurrence of the retention mixer: linear attention with one fixed decay per head and no softmax.
+//
+//   per head, S [key channel, value channel] (stored per value channel, a column contiguous):
+//     S_t = d S_t-1 + k_t v_t^T;   o_t = S_t^T q_t = d (S_t-1^T q_t) + (q_t . k_t) v_t
+//   q and k are the projections' results rotated by the token's position (half-split pairs i, i + r/2 of the first r
+//   channels; angle = position * inv_freq[i], a 32-bit product), k also times key_scale, both in 32-bit while a chunk
+//   of tokens is staged in shared memory: nothing rotated is ever rounded to the storage type.
+// The decay, the rotation, the state and every sum are 32-bit; T is the storage type of the projections' results.
+// One lane count and one order of sums for every shape of step: a request's 32-bit results do not depend on how it was
+// cut into steps.  A row of a captured decode batch whose position is negative is padding: nothing is read or written.
+#include "common.cuh"
+
+using namespace mir;
+
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kLanes = 8;                                        // lanes that share one column of the state
+
+// blockDim (32, kWarps), grid (rows, heads, ceil(value_dim / (kWarps * 4))).  Lane l of a column holds the key
+// channels 4 (m kLanes + l) .. + 3, m < PER / 4.  The inputs of CHUNK tokens at a time are staged in shared memory
+// (every column of a head reads the same q and k): a warp stages whole tokens, rotating as it goes, and leaves the
+// token's q . k beside them.  What the next chunk needs is fetched into registers before the walk over the current
+// chunk starts.  SHORT: a step of single tokens stages one token a warp.
+template <typename T, int PER, bool SHORT>
+__global__ void __launch_bounds__(kWarps * 32)
+retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long long ld,
+                      const float* __restrict__ inv_freq, int rotary_dim, const float* __restrict__ decays,
+                      float key_scale, float* __restrict__ state, const int* __restrict__ query_starts,
+                      const int* __restrict__ state_slots, const int* __restrict__ positions, float* __restrict__ out,
+                      int heads, int dim, int value_dim) {
+  constexpr int COLUMNS = 32 / kLanes;
+  constexpr int BLOCK_COLUMNS = COLUMNS * kWarps;
+  constexpr int PADDED = kLanes * PER;
+  constexpr int ROW = 2 * PADDED + 4 + BLOCK_COLUMNS;             // q | k | q . k | v of this CTA's columns
+  constexpr int CHUNK = SHORT ? kWarps : (PER <= 8 ? 32 : (PER <= 16 ? 16 : 8));
+  __shared__ __align__(16) float staged[CHUNK * ROW];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int lane = threadIdx.x, warp = threadIdx.y;
+  const int thread = warp * 32 + lane;
+  const int l = lane % kLanes;
+  const int row = blockIdx.x, head = blockIdx.y;
+  const int first_column = blockIdx.z * BLOCK_COLUMNS;
+  const int local_column = warp * COLUMNS + lane / kLanes;
+  const int column = first_column + local_column;
+  const int start = query_starts[row], end = query_starts[row + 1];
+  if (end <= start || positions[start] < 0) return;              // the whole CTA: an empty or padding row
+  const bool active = column < value_dim;
+  const bool wide = dim % 4 == 0;
+  const float decay = decays[head];
+  const int half = rotary_dim / 2;
+  float* column_state = state + (((size_t)state_slots[row] * heads + head) * value_dim + (active ? column : 0)) * dim;
+
+  float s[PER];
+#pragma unroll
+  for (int m = 0; m < PER; m += 4) {
+    const int i = (m / 4 * kLanes + l) * 4;
+    if (wide) {
+      const float4 piece = (active && i < dim) ? *reinterpret_cast<const float4*>(column_state + i)
+                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+      s[m] = piece.x; s[m + 1] = piece.y; s[m + 2] = piece.z; s[m + 3] = piece.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[m + e] = (active && i + e < dim) ? column_state[i + e] : 0.0f;
+    }
+  }
+  const size_t key_at = (size_t)head * dim, value_at = (size_t)head * value_dim;
+  constexpr int TOKENS_PER_WARP = CHUNK / kWarps;
+  constexpr int PER_LANE = PADDED / 32;
+  constexpr int VALUES_PER_THREAD = (CHUNK * BLOCK_COLUMNS + kWarps * 32 - 1) / (kWarps * 32);
+  float next_q[TOKENS_PER_WARP][PER_LANE], next_k[TOKENS_PER_WARP][PER_LANE];
+  float next_v[VALUES_PER_THREAD];
+  auto fetch = [&](int from) {
+    const int count = min(CHUNK, end - from);
+#pragma unroll
+    for (int tt = 0; tt < TOKENS_PER_WARP; ++tt) {
+      const int t = warp + tt * kWarps;
+      const float position = t < count ? (float)positions[from + t] : 0.0f;
+#pragma unroll
+      for (int e = 0; e < PER_LANE; ++e) {
+        const int i = lane + 32 * e;
+        next_q[tt][e] = 0.0f; next_k[tt][e] = 0.0f;
+        if (t < count && i < dim) {
+          const size_t source = (size_t)(from + t) * ld + key_at;
+          float qi = to_float(q[source + i]), ki = to_float(k[source + i]);
+          if (i < rotary_dim) {
+            // the first of a pair becomes u cos - v sin, the second v cos + u sin
+            const bool first = i < half;
+            const int partner = first ? i + half : i - half;
+            const float qp = to_float(q[source + partner]), kp = to_float(k[source + partner]);
+            float sine, cosine;
+            sincosf(position * inv_freq[first ? i : partner], &sine, &cosine);
+            qi = first ? qi * cosine - qp * sine : qi * cosine + qp * sine;
+            ki = first ? ki * cosine - kp * sine : ki * cosine + kp * sine;
+          }
+          next_q[tt][e] = qi;
+          next_k[tt][e] = ki * key_scale;
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < VALUES_PER_THREAD; ++j) {
+      const int index = thread + j * kWarps * 32;
+      const int t = index / BLOCK_COLUMNS, c = index - t * BLOCK_COLUMNS;
+      next_v[j] = (t < count && first_column + c < value_dim)
+                      ? to_float(v[(size_t)(from + t) * ld + value_at + first_column + c]) : 0.0f;
+    }
+  };
+  auto commit = [&](int from) {
+    const int count = min(CHUNK, end - from);
+#pragma unroll
+    for (int tt = 0; tt < TOKENS_PER_WARP; ++tt) {
+      const int t = warp + tt * kWarps;
+      if (t >= count) continue;                                  // (the same for the whole warp)
+      float* at = staged + t * ROW;
+      float sum = 0.0f;
+#pragma unroll
+      for (int e = 0; e < PER_LANE; ++e) {
+        const int i = lane + 32 * e;
+        sum = fmaf(next_q[tt][e], next_k[tt][e], sum);
+        at[i] = next_q[tt][e]; at[PADDED + i] = next_k[tt][e];
+      }
+      sum = warp_sum(sum);
+      if (lane == 0) at[2 * PADDED] = sum;
+    }
+#pragma unroll
+    for (int j = 0; j < VALUES_PER_THREAD; ++j) {
+      const int index = thread + j * kWarps * 32;
+      const int t = index / BLOCK_COLUMNS, c = index - t * BLOCK_COLUMNS;
+      if (t < CHUNK) staged[t * ROW + 2 * PADDED + 4 + c] = next_v[j];
+    }
+  };
+  fetch(start);
+  const size_t out_width = (size_t)heads * value_dim;
+  for (int from = start; from < end; from += CHUNK) {
+    const int count = min(CHUNK, end - from);
+    __syncthreads();                                             // the chunk before has been read
+    commit(from);
+    __syncthreads();
+    if (from + CHUNK < end) fetch(from + CHUNK);
+    const float* in = staged - ROW;
+#pragma unroll 2
+    for (int t = 0; t < count; ++t) {
+      in += ROW;
+      const float value = in[2 * PADDED + 4 + local_column];
+      float read[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int m = 0; m < PER; m += 4) {
+        const int i = (m / 4 * kLanes + l) * 4;
+        const float4 query = *reinterpret_cast<const float4*>(in + i);
+        const float4 key = *reinterpret_cast<const float4*>(in + PADDED + i);
+        read[0] = fmaf(s[m], query.x, read[0]);
+        read[1] = fmaf(s[m + 1], query.y, read[1]);
+        read[2] = fmaf(s[m + 2], query.z, read[2]);
+        read[3] = fmaf(s[m + 3], query.w, read[3]);
+        s[m] = fmaf(s[m], decay, key.x * value);
+        s[m + 1] = fmaf(s[m + 1], decay, key.y * value);
+        s[m + 2] = fmaf(s[m + 2], decay, key.z * value);
+        s[m + 3] = fmaf(s[m + 3], decay, key.w * value);
+      }
+      float total = (read[0] + read[1]) + (read[2] + read[3]);
+      total += __shfl_xor_sync(0xffffffffu, total, 1);
+      total += __shfl_xor_sync(0xffffffffu, total, 2);
+      total += __shfl_xor_sync(0xffffffffu, total, 4);
+      if (l == 0 && active)
+        out[(size_t)(from + t) * out_width + value_at + column] = fmaf(in[2 * PADDED], value, decay * total);
+    }
+  }
+  if (!active) return;
+#pragma unroll
+  for (int m = 0; m < PER; m += 4) {
+    const int i = (m / 4 * kLanes + l) * 4;
+    if (wide) {
+      if (i < dim) *reinterpret_cast<float4*>(column_state + i) = make_float4(s[m], s[m + 1], s[m + 2], s[m + 3]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (i + e < dim) column_state[i + e] = s[m + e];
+    }
+  }
+}
+
+template <typename T, int PER, bool SHORT>
+int launch_scan(cudaStream_t stream, const void* q, const void* k, const void* v, long long ld, const float* inv_freq,
+                int rotary_dim, const float* decays, float key_scale, float* state, const int* query_starts,
+                const int* state_slots, const int* positions, float* out, int rows, int heads, int dim, int value_dim) {
+  constexpr int columns = kWarps * (32 / kLanes);
+  return mir_launch("retention_scan", retention_scan_kernel<T, PER, SHORT>,
+                    dim3(rows, heads, (value_dim + columns - 1) / columns), dim3(32, kWarps), 0, stream, 0, (const T*)q,
+                    (const T*)k, (const T*)v, ld, inv_freq, rotary_dim, decays, key_scale, state, query_starts,
+                    state_slots, positions, out, heads, dim, value_dim);
+}
+
+template <typename T>
+int launch_scan_for(cudaStream_t stream, const void* q, const void* k, const void* v, long long ld,
+                    const float* inv_freq, int rotary_dim, const float* decays, float key_scale, float* state,
+                    const int* query_starts, const int* state_slots, const int* positions, float* out, int rows,
+                    int heads, int dim, int value_dim, bool single_tokens) {
+#define MIR_RETENTION(P)                                                                                            \
+  if (single_tokens)                                                                                                \
+    return launch_scan<T, P, true>(stream, q, k, v, ld, inv_freq, rotary_dim, decays, key_scale, state,            \
+                                   query_starts, state_slots, positions, out, rows, heads, dim, value_dim);        \
+  return launch_scan<T, P, false>(stream, q, k, v, ld, inv_freq, rotary_dim, decays, key_scale, state, query_starts, \
+                                  state_slots, positions, out, rows, heads, dim, value_dim);
+  if (dim <= 32) { MIR_RETENTION(4) }
+  if (dim <= 64) { MIR_RETENTION(8) }
+  if (dim <= 96) { MIR_RETENTION(12) }
+  if (dim <= 128) { MIR_RETENTION(16) }
+  if (dim <= 192) { MIR_RETENTION(24) }
+  if (dim <= 256) { MIR_RETENTION(32) }
+#undef MIR_RETENTION
+  mir_set_error("retention_scan: heads of %d key channels are wider than 256", dim);
+  return MIR_BAD_ARGUMENT;
+}
+
+}  // namespace
+
+// q, k [tokens, heads * dim] and v [tokens, heads * value_dim] with one row stride ld in the activations' type (views
+// of one packed projection); inv_freq [rotary_dim / 2] 32-bit (may be null with rotary_dim 0); decays [heads] 32-bit;
+// state [slots, heads, value_dim, dim] 32-bit; out [tokens, heads * value_dim] 32-bit: o before the head norm.
+MIR_EXPORT int mir_retention_scan(int bf16, const void* q, const void* k, const void* v, long long ld,
+                                  const float* inv_freq, int rotary_dim, const float* decays, float key_scale,
+                                  float* state, const int* query_starts, const int* state_slots, const int* positions,
+                                  float* out, int tokens, int rows, int heads, int dim, int value_dim,
+                                  cudaStream_t stream) {
+  if (tokens == 0 || rows == 0) return MIR_OK;
+  if (tokens < 0 || rows < 0 || heads <= 0 || dim <= 0 || value_dim <= 0 || heads > 65535 || rotary_dim < 0 ||
+      rotary_dim > dim || (rotary_dim & 1) || (rotary_dim > 0 && inv_freq == nullptr)) {
+    mir_set_error("retention_scan: bad sizes (tokens %d, rows %d, heads %d, dim %d, value_dim %d, rotary_dim %d)",
+                  tokens, rows, heads, dim, value_dim, rotary_dim);
+    return MIR_BAD_ARGUMENT;
+  }
+  const bool single_tokens = tokens == rows;                     // a step of decoded tokens: every row brings one
+  if (bf16)
+    return launch_scan_for<__nv_bfloat16>(stream, q, k, v, ld, inv_freq, rotary_dim, decays, key_scale, state,
+                                          query_starts, state_slots, positions, out, rows, heads, dim, value_dim,
+                                          single_tokens);
+  return launch_scan_for<float>(stream, q, k, v, ld, inv_freq, rotary_dim, decays, key_scale, state, query_starts,
+                                state_slots, positions, out, rows, heads, dim, value_dim, single_tokens);
+}

@@ -30,10 +30,10 @@ _SIGNATURES = {
         "mir_add_bias": [c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "mir_cast": [c_int, c_void_p, c_void_p, c_size_t, c_void_p],
         "mir_qk_rope_store": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+                              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_longlong, c_int, c_void_p],
         "mir_paged_attention_generic": [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                                        c_int, c_int, c_void_p],
+                                        c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p],
         "mir_embed_pairs": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                             c_longlong, c_longlong, c_float, c_void_p],
         "mir_gelu_tanh": [c_int, c_void_p, c_size_t, c_void_p],
@@ -61,6 +61,9 @@ _SIGNATURES = {
                             c_longlong, c_int, c_int, c_int, c_int, c_void_p],
         "mir_wkv_mix": [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                         c_int, c_int, c_int, c_int, c_void_p],
+        "mir_retention_scan": [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_float,
+                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                               c_void_p],
         "mir_wkv_scan": [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "mir_moe_route": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -525,6 +528,14 @@ def tanh(x: torch.Tensor) -> None:
     _check(lib, lib.mir_activation(2, _is_bf16(x), x.data_ptr(), x.numel(), _stream()))
 
 
+def relu_squared(x: torch.Tensor) -> None:
+    """x <- max(x, 0)^2 in place, computed in 32-bit."""
+    _cuda(x)
+    _require(x.is_contiguous(), "relu_squared: a contiguous tensor is needed")
+    lib = library("core")
+    _check(lib, lib.mir_activation(3, _is_bf16(x), x.data_ptr(), x.numel(), _stream()))
+
+
 def softcap(logits: torch.Tensor, cap: float) -> None:
     """logits <- cap * tanh(logits / cap) in place on contiguous 32-bit logits."""
     _cuda(logits)
@@ -748,6 +759,37 @@ def wkv_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_raw: torch
                                  _stream()))
 
 
+# --------------------------------------------------------------------------- retention
+def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, inv_freq: Optional[torch.Tensor],
+                   decays: torch.Tensor, key_scale: float, state: torch.Tensor, query_starts: torch.Tensor,
+                   state_slots: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, heads: int, dim: int,
+                   value_dim: int) -> None:
+    """The retention recurrence over the tokens of each request row, from and into state [slots, heads, value_dim, dim]
+    (32-bit): per head S <- decay_h S + k v^T, o = S^T q, with q and k rotated by the token's position (half-split pairs
+    of the first 2 * len(inv_freq) channels, 32-bit angles) and k times `key_scale` after the rotation.  q, k [tokens,
+    heads * dim] and v [tokens, heads * value_dim]: views with one row stride in the activations' dtype; decays 32-bit
+    [heads]; out 32-bit [tokens, heads * value_dim]."""
+    _cuda(q, k, v, inv_freq, decays, state, query_starts, state_slots, positions, out)
+    tokens = q.shape[0]
+    rows = query_starts.numel() - 1
+    rotary = 0 if inv_freq is None else 2 * inv_freq.numel()
+    _require(q.shape == (tokens, heads * dim) and k.shape == q.shape and v.shape == (tokens, heads * value_dim)
+             and all(t.stride(1) == 1 and t.stride(0) == q.stride(0) and t.dtype == q.dtype for t in (q, k, v)),
+             "retention_scan: q, k, v are views with one row stride and dtype")
+    _require(out.dtype == torch.float32 and out.is_contiguous() and out.shape == (tokens, heads * value_dim)
+             and decays.dtype == torch.float32 and decays.is_contiguous() and decays.numel() == heads
+             and state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (heads, value_dim, dim)
+             and (inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.is_contiguous() and rotary <= dim)),
+             "retention_scan: decays, state and out are contiguous float32 of the stated shapes")
+    _require(all(t.dtype == torch.int32 for t in (query_starts, state_slots, positions)),
+             "retention_scan: the batch description is int32")
+    lib = library("core")
+    _check(lib, lib.mir_retention_scan(_is_bf16(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0),
+                                       _ptr(inv_freq), rotary, decays.data_ptr(), float(key_scale), state.data_ptr(),
+                                       query_starts.data_ptr(), state_slots.data_ptr(), positions.data_ptr(),
+                                       out.data_ptr(), tokens, rows, heads, dim, value_dim, _stream()))
+
+
 # --------------------------------------------------------------------------- routed experts
 def moe_route(logits: torch.Tensor, correction: Optional[torch.Tensor], has_gate: bool, ids: torch.Tensor,
               weights: torch.Tensor, shared_gate: Optional[torch.Tensor], experts: int, top: int, groups: int, keep: int,
@@ -968,15 +1010,19 @@ def qk_rope_store(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Opti
                   inv_freq: Optional[torch.Tensor], q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor],
                   k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], heads: int, kv_heads: int,
                   head_dim: int, rotary_dim: int, eps: float, write_kv: bool = True,
-                  keys_in_place: bool = False, value_dim: Optional[int] = None) -> None:
+                  keys_in_place: bool = False, value_dim: Optional[int] = None, interleaved: bool = False,
+                  queries_only: bool = False) -> None:
     """q/k-norm + rotary on the packed qkv rows in place for q, k and v into their pages.  `keys_in_place`:
-    the keys are normed and rotated in place like the queries and nothing is written to the pages."""
-    write_kv = write_kv and not keys_in_place
+    the keys are normed and rotated in place like the queries and nothing is written to the pages.  `interleaved`:
+    the rotation pairs dims 2i and 2i + 1.  The rows may be wider than q, k and v (what lies behind them is left
+    alone); `queries_only`: they start with the query heads and hold no keys or values."""
+    write_kv = write_kv and not keys_in_place and not queries_only
     _cuda(qkv, positions, slot_mapping, inv_freq, q_norm, k_norm, k_pages, v_pages)
     tokens = qkv.shape[0]
     value_dim = head_dim if value_dim is None else value_dim
-    _require(qkv.is_contiguous() and qkv.shape[1] == (heads + kv_heads) * head_dim + kv_heads * value_dim,
-             "qk_rope_store: bad qkv")
+    packed = heads * head_dim if queries_only else (heads + kv_heads) * head_dim + kv_heads * value_dim
+    _require(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= packed and qkv.stride(0) >= qkv.shape[1]
+             and not (keys_in_place and queries_only), "qk_rope_store: bad qkv")
     _require(positions.dtype == torch.int32 and positions.numel() >= tokens, "qk_rope_store: bad positions")
     if rotary_dim:
         _require(inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2,
@@ -992,21 +1038,29 @@ def qk_rope_store(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Opti
     _check(lib, lib.mir_qk_rope_store(_is_bf16(qkv), qkv.data_ptr(), positions.data_ptr(), _ptr(slot_mapping),
                                       _ptr(inv_freq), _ptr(q_norm), _ptr(k_norm), _ptr(k_pages), _ptr(v_pages),
                                       tokens, heads, kv_heads, head_dim, value_dim, rotary_dim, eps,
-                                      2 if keys_in_place else int(write_kv), _stream()))
+                                      2 if keys_in_place else int(write_kv), int(interleaved), qkv.stride(0),
+                                      int(queries_only), _stream()))
 
 
 def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                             block_table: torch.Tensor, row_of_token: torch.Tensor, positions: torch.Tensor,
                             page_size: int, heads: int, kv_heads: int, head_dim: int, scale: float,
                             window: Optional[int], value_dim: Optional[int] = None, keep_first: int = 0,
-                            values_in_keys: bool = False) -> None:
+                            values_in_keys: bool = False, sinks: Optional[torch.Tensor] = None,
+                            gate: Optional[torch.Tensor] = None) -> None:
     """out[t, h] = softmax over the visible cached keys of token t's request; q is read from the packed qkv rows.
     `value_dim`: width of a value head (head_dim if None); `keep_first`: with a window, the request's first keys
     that stay visible to every query; `values_in_keys`: a value is the first value_dim elements of its key (a cached
-    latent that is read both ways) and v_pages is not looked at."""
+    latent that is read both ways) and v_pages is not looked at.  `sinks` (float32 [heads]): exp(sink_h) joins the
+    denominator of head h's softmax.  `gate` ([tokens, heads * value_dim] view, unit column stride, out's dtype): the
+    result is multiplied by its sigmoid."""
     if values_in_keys:
         v_pages = k_pages
-    _cuda(qkv, out, k_pages, v_pages, block_table, row_of_token, positions)
+    _cuda(qkv, out, k_pages, v_pages, block_table, row_of_token, positions, sinks, gate)
+    _require(sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == heads and sinks.is_contiguous()),
+             "paged_attention: sinks are float32 [heads]")
+    _require(gate is None or (gate.dtype == out.dtype and gate.shape == out.shape and gate.stride(1) == 1),
+             "paged_attention: the gate has out's shape and dtype")
     tokens = out.shape[0]
     value_dim = head_dim if value_dim is None else value_dim
     _require(out.is_contiguous() and out.shape[1] == heads * value_dim and qkv.dtype == out.dtype
@@ -1018,7 +1072,7 @@ def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch
         _is_bf16(out), qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], row_of_token.data_ptr(), positions.data_ptr(), tokens,
         page_size, heads, kv_heads, head_dim, value_dim, scale, int(window or 0), int(keep_first or 0),
-        head_dim if values_in_keys else 0, _stream()))
+        head_dim if values_in_keys else 0, _ptr(sinks), _ptr(gate), gate.stride(0) if gate is not None else 0, _stream()))
 
 
 FAST_HEAD_DIMS = (64, 128)      # what the tensor-core attention kernels take; other sizes use the reference kernel
@@ -1257,6 +1311,23 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tens
         status = call(lazy.materialize(alloc), None)
     _check(lib, status)
     return bool(wrote.value)
+
+
+ACTIVATIONS = ("gelu_tanh", "gelu_erf", "relu2")      # what linear_act applies to a product's result
+
+
+def linear_act(x, weight: torch.Tensor, out: torch.Tensor, activation: str, alloc=None) -> None:
+    """out = act(x . weight^T) in the activations' dtype, act one of ACTIVATIONS: the two GELU forms as linear_gelu
+    runs them; "relu2" (the square of relu) as the product and the activation's kernel."""
+    if activation == "relu2":
+        if isinstance(x, NormedResidual):
+            x = x.materialize(alloc)
+        linear(x, weight, out, alloc=alloc)
+        _require(out.is_contiguous(), "linear_act: a contiguous result is needed")
+        relu_squared(out)
+        return
+    _require(activation in ACTIVATIONS, f"linear_act: unknown activation {activation!r}")
+    linear_gelu(x, weight, out, alloc=alloc, exact=activation == "gelu_erf")
 
 
 def linear_gelu(x, weight: torch.Tensor, out: torch.Tensor, alloc=None, exact: bool = False) -> None:

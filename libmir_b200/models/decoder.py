@@ -38,6 +38,7 @@ class DecoderModel:
         self.env = env
         self.blocks = [build_block(layer, env) for layer in spec.layers]
         self.final_norm = build_part(spec.final_norm, env)
+        self.embedding_norm = build_part(spec.embedding.norm, env) if spec.embedding.norm is not None else None
         self.embedding: Optional[torch.Tensor] = None
         self.pair_embedding: Optional[torch.Tensor] = None      # the table of token pairs, if the model has one
         self.loop_steps: Optional[torch.Tensor] = None          # [passes, hidden] 32-bit: what each pass of a loop adds
@@ -46,17 +47,32 @@ class DecoderModel:
 
     # -- what the cache manager must provide ------------------------------------
     def cache_plan(self) -> List[CacheEntryPlan]:
-        plan = []
-        for index, entry in enumerate(self.spec.schedule):
-            requirement = self.blocks[entry.layer].cache_requirement()
-            if entry.cache_of is not None:
-                other = self.blocks[self.spec.schedule[entry.cache_of].layer].cache_requirement()
-                if other != requirement:
+        """An entry that reads another's cache must ask for the same shape; its window may differ, and the entry that
+        owns the pages then keeps what the widest of them sees (every token, if one of them has no window)."""
+        from dataclasses import replace
+        schedule = self.spec.schedule
+        needs = [self.blocks[entry.layer].cache_requirement() for entry in schedule]
+        for index, entry in enumerate(schedule):
+            if entry.cache_of is None:
+                continue
+            mine, other = needs[index], needs[entry.cache_of]
+            if isinstance(mine, PagedKv) and isinstance(other, PagedKv):
+                if replace(mine, window=None, keep_first=0) != replace(other, window=None, keep_first=0):
                     raise ValueError(f"schedule entry {index} reads the cache of entry {entry.cache_of}, whose shape "
-                                     f"{other} differs from its own {requirement}")
-                plan.append(CacheEntryPlan(index, requirement, entry.cache_of, False))
+                                     f"{other} differs from its own {mine}")
+                if mine.window != other.window or mine.keep_first != other.keep_first:
+                    widest = None if None in (mine.window, other.window) else max(mine.window, other.window)
+                    kept = max(mine.keep_first, other.keep_first) if widest is not None else 0
+                    needs[entry.cache_of] = replace(other, window=widest, keep_first=kept)
+            elif other != mine:
+                raise ValueError(f"schedule entry {index} reads the cache of entry {entry.cache_of}, whose shape "
+                                 f"{other} differs from its own {mine}")
+        plan = []
+        for index, entry in enumerate(schedule):
+            if entry.cache_of is not None:
+                plan.append(CacheEntryPlan(index, needs[entry.cache_of], entry.cache_of, False))
             else:
-                plan.append(CacheEntryPlan(index, requirement, index, True))
+                plan.append(CacheEntryPlan(index, needs[index], index, True))
         return plan
 
     # -- parameters ---------------------------------------------------------------
@@ -77,6 +93,9 @@ class DecoderModel:
                     table[layer_spec.prefix + layer_spec.names[slot] + local] = (part, local, param)
         for local, param in self.final_norm.parameters().items():
             table[spec.final_norm_name + local] = (self.final_norm, local, param)
+        if self.embedding_norm is not None:
+            for local, param in self.embedding_norm.parameters().items():
+                table[spec.embedding.norm_name + local] = (self.embedding_norm, local, param)
         if not spec.head.tied:
             table[spec.head.name] = (self, "head", ParamSpec((spec.head.vocab_size, spec.head.hidden_size)))
         return table
@@ -112,6 +131,8 @@ class DecoderModel:
         for block in self.blocks:
             out.extend(part for _, part in block.parts())
         out.append(self.final_norm)
+        if self.embedding_norm is not None:
+            out.append(self.embedding_norm)
         return out
 
     def portion_multiple(self) -> int:
@@ -148,6 +169,8 @@ class DecoderModel:
                                 pairs.mul_previous, pairs.mul_current, spec.embedding.multiplier)
         else:
             kernels.embed(self.embedding, ctx.tokens, residual, spec.embedding.multiplier)
+        if self.embedding_norm is not None:                  # the stream starts from the normed rows, in 32-bit
+            self.embedding_norm.forward(ctx, residual, out=residual)
         embedded = None
         if spec.loop is not None and spec.loop.add_embedding and any((e.opens_pass or 0) > 0 for e in spec.schedule):
             embedded = ctx.alloc(tuple(residual.shape), torch.float32)       # later passes add the embedding's output again

@@ -3,11 +3,12 @@
 from ..registry import register_part
 from .attention import SoftmaxAttention
 from .base import Block, BuildEnv, FeedForward, Mixer, Norm, Part, PartContext, Position, ScratchContext
-from .block import ARRANGEMENTS, ParallelBlock, PreNormBlock, build_block
+from .block import ARRANGEMENTS, OutputNormBlock, ParallelBlock, PreNormBlock, build_block
 from .delta_rule import GatedDeltaRule
 from .experts import RoutedExperts
 from .feed_forward import GeluMlp, SwiGlu
 from .latent_attention import LatentAttention
+from .retention import Retention
 from .wkv import Wkv
 from .side_by_side import SideBySide
 from .norm import RmsNorm
@@ -22,8 +23,9 @@ register_part("gated_delta_rule", GatedDeltaRule)
 register_part("side_by_side", SideBySide)
 register_part("latent_attention", LatentAttention)
 register_part("wkv", Wkv)
+register_part("retention", Retention)
 register_part("routed_experts", RoutedExperts)
 
 __all__ = ["ARRANGEMENTS", "Block", "BuildEnv", "FeedForward", "GatedDeltaRule", "GeluMlp", "LatentAttention", "Mixer", "Norm",
-           "ParallelBlock", "Part", "PartContext", "Position", "PreNormBlock", "RmsNorm", "Rotary", "RoutedExperts",
+           "OutputNormBlock", "ParallelBlock", "Part", "PartContext", "Position", "PreNormBlock", "Retention", "RmsNorm", "Rotary", "RoutedExperts",
            "ScratchContext", "SideBySide", "SoftmaxAttention", "SwiGlu", "Wkv", "build_block", "inverse_frequencies"]

@@ -11,6 +11,11 @@ x + mixer(h) + feed_forward(h) is formed in 32-bit whatever the engine's dtype.
 With a second norm (`feed_forward_norm`): x += mixer(norm_1(x)) + feed_forward(norm_2(x)), both norms of the same x:
 both are computed before either branch adds into the residual, by one kernel where they are RMS norms with one eps
 (one root mean square, two weights).
+
+output_norm:  x += m * norm_1(mixer(x));  x += m * norm_2(feed_forward(x))
+Each branch reads the residual itself (cast to the engine's dtype) and its RESULT goes through the norm: the branch
+writes its result into a 32-bit buffer, and one kernel norms that buffer and adds m times it into the residual, so
+the norm and the residual sum are 32-bit.  m is LayerSpec.residual_scale.
 """
 
 from __future__ import annotations
@@ -178,7 +183,46 @@ class ParallelBlock(Block):
         ctx.upcoming_norm = None
 
 
-ARRANGEMENTS = {"pre_norm": PreNormBlock, "parallel": ParallelBlock}
+class OutputNormBlock(Block):
+    """x += m * norm_1(mixer(x)), then x += m * norm_2(feed_forward(x)): the norms stand on the branches' results."""
+
+    SLOTS = ("mixer_norm", "mixer", "feed_forward_norm", "feed_forward")
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        from .norm import RmsNorm
+        self.mixer_norm = build_part(spec.mixer_norm, env)
+        self.mixer = build_part(spec.mixer, env)
+        self.feed_forward_norm = build_part(spec.feed_forward_norm, env)
+        self.feed_forward = build_part(spec.feed_forward, env)
+        for norm, branch in ((self.mixer_norm, self.mixer), (self.feed_forward_norm, self.feed_forward)):
+            if branch is not None and type(norm) is not RmsNorm:
+                raise ValueError("the output_norm arrangement takes an RMS norm behind every branch")
+        self.scale = float(spec.residual_scale)
+
+    def parts(self):
+        return [(slot, getattr(self, slot)) for slot in self.SLOTS if getattr(self, slot) is not None]
+
+    def cache_requirement(self):
+        return self.mixer.cache_requirement()
+
+    def forward(self, ctx, cache, residual):
+        from .. import kernels
+        ctx.upcoming_norm = None             # no norm reads the residual: nothing for a product to prepare
+        ctx.residual_stats = None
+        x = ctx.cast_residual(residual)
+        result = ctx.alloc(tuple(residual.shape), torch.float32)
+        self.mixer.forward(ctx, cache, x, result, overwrite=True)
+        kernels.add_normed_branches([result], [self.mixer_norm.weight], residual, self.mixer_norm.spec.eps, self.scale)
+        if self.feed_forward is not None:
+            x = ctx.cast_residual(residual)
+            self.feed_forward.forward(ctx, x, result, overwrite=True)
+            kernels.add_normed_branches([result], [self.feed_forward_norm.weight], residual,
+                                        self.feed_forward_norm.spec.eps, self.scale)
+        ctx.residual_stats = None
+
+
+ARRANGEMENTS = {"pre_norm": PreNormBlock, "parallel": ParallelBlock, "output_norm": OutputNormBlock}
 
 
 def build_block(layer_spec, env):

@@ -47,16 +47,16 @@ class SwiGlu(FeedForward):
 
 
 class GeluMlp(FeedForward):
-    """down(gelu(up(x))), accumulated into the 32-bit residual.  The activation is computed in 32-bit: the tanh form
-    or the exact (erf) form, in the epilogue of the up projection where our own products run it, else on the
-    product's rows, in place."""
+    """down(act(up(x))), accumulated into the 32-bit residual.  The activation is computed in 32-bit: the tanh form
+    of the GELU, its exact (erf) form, or the square of relu, in the epilogue of the up projection where our own
+    products run it, else on the product's rows, in place."""
 
     graph_safe = True
     takes_normed_residual = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
-        if spec.activation not in ("gelu_tanh", "gelu_erf"):
+        if spec.activation not in kernels.ACTIVATIONS:
             raise ValueError(f"unknown activation {spec.activation!r}")
         self.w_up = self.w_down = None
 
@@ -72,8 +72,13 @@ class GeluMlp(FeedForward):
     def weight_bytes(self):
         return (self.w_up.numel() + self.w_down.numel()) * self.w_down.element_size()
 
-    def forward(self, ctx, x, residual):
+    def forward(self, ctx, x, residual, overwrite=False):
+        """residual += down(act(up(x))); with `overwrite` the result replaces `residual` (a 32-bit buffer of an
+        arrangement that norms the branch's result) instead of being added to it."""
         hidden = ctx.alloc((x.shape[0], self.spec.intermediate_size), self.env.dtype)   # (x may be a folded norm)
         # the activation in the product's epilogue
-        kernels.linear_gelu(x, self.w_up, hidden, alloc=ctx.alloc, exact=self.spec.activation == "gelu_erf")
-        ctx.accumulate(hidden, self.w_down, residual)
+        kernels.linear_act(x, self.w_up, hidden, self.spec.activation, alloc=ctx.alloc)
+        if overwrite:
+            kernels.linear(hidden, self.w_down, residual, alloc=ctx.alloc)
+        else:
+            ctx.accumulate(hidden, self.w_down, residual)
