@@ -235,7 +235,7 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
                         const int* __restrict__ positions, int page_size, int heads, int kv_heads, float scale_log2,
                         int window, int partition, int num_partitions, int part_slow, float* __restrict__ partial_o,
                         float* __restrict__ partial_ml, bf16* __restrict__ out, int keep_first,
-                        int* __restrict__ virtual_positions) {
+                        int* __restrict__ virtual_positions, AttentionExtras extras) {
   constexpr int STRIDE = D + 8;
   constexpr int TILE_ELEMS = kDecodeTile * STRIDE;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -435,7 +435,9 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
     }
     const size_t head = (size_t)row * heads + head0 + r;
     if (num_partitions == 1) {
-      out[head * D + d] = __float2bfloat16_rn(denom > 0.0f ? acc / denom : 0.0f);
+      if (denom > 0.0f) denom += sink_term(extras, head0 + r, top);
+      out[head * D + d] = __float2bfloat16_rn(
+          denom > 0.0f ? acc / denom * gate_factor(extras, row, (size_t)(head0 + r) * D + d) : 0.0f);
     } else {
       partial_o[(head * num_partitions + part) * D + d] = acc;
       if (d == 0) {
@@ -456,7 +458,7 @@ template <int D>
 __global__ void __launch_bounds__(kMergeWarps * 32)
 decode_merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                     const int* __restrict__ positions, int heads, int window, int partition, int num_partitions,
-                    bf16* __restrict__ out) {
+                    bf16* __restrict__ out, AttentionExtras extras) {
   constexpr int LANES = D / 4;                                 // lanes of a warp that hold elements
   __shared__ float warp_top[kMergeWarps];
   __shared__ float sums[kMergeWarps][D + 1];                   // [warp][elements, then the denominator]
@@ -519,8 +521,8 @@ decode_merge_kernel(const float* __restrict__ partial_o, const float* __restrict
   __syncthreads();
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     const float total = (sums[0][d] + sums[1][d]) + (sums[2][d] + sums[3][d]);
-    const float all = (sums[0][D] + sums[1][D]) + (sums[2][D] + sums[3][D]);
-    out[index * D + d] = __float2bfloat16_rn(all > 0.0f ? total / all : 0.0f);
+    const float all = (sums[0][D] + sums[1][D]) + (sums[2][D] + sums[3][D]) + sink_term(extras, head, top);
+    out[index * D + d] = __float2bfloat16_rn(all > 0.0f ? total / all * gate_factor(extras, row, (size_t)head * D + d) : 0.0f);
   }
   if (threadIdx.x == 0) MIR_TRACE_POINT(merge, 2);
 }
@@ -533,7 +535,7 @@ template <int D>
 __global__ void __launch_bounds__(kMergeWarps * 32)
 decode_merge_few_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                         const int* __restrict__ positions, int heads, int window, int partition, int num_partitions,
-                        bf16* __restrict__ out) {
+                        bf16* __restrict__ out, AttentionExtras extras) {
   constexpr int PER = D / 32;                                  // elements per lane: 4 or 2
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.x * kMergeWarps + warp, row = blockIdx.y;
@@ -590,10 +592,13 @@ decode_merge_few_kernel(const float* __restrict__ partial_o, const float* __rest
     for (int j = 0; j < PER; ++j) acc[j] += piece[i][j] * w;
     denom += denominators[i] * w;
   }
+  denom += sink_term(extras, head, top);
+#pragma unroll
+  for (int j = 0; j < PER; ++j)
+    acc[j] = denom > 0.0f ? acc[j] / denom * gate_factor(extras, row, (size_t)head * D + PER * lane + j) : 0.0f;
 #pragma unroll
   for (int j = 0; j < PER; j += 2)
-    *reinterpret_cast<__nv_bfloat162*>(dst + j) =
-        __floats2bfloat162_rn(denom > 0.0f ? acc[j] / denom : 0.0f, denom > 0.0f ? acc[j + 1] / denom : 0.0f);
+    *reinterpret_cast<__nv_bfloat162*>(dst + j) = __floats2bfloat162_rn(acc[j], acc[j + 1]);
   if (threadIdx.x == 0) MIR_TRACE_POINT(merge, 2);
 }
 
@@ -608,7 +613,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, size_t q_stride, bf16* __re
                          const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                          const int* __restrict__ block_table, int table_width, const int* __restrict__ query_starts,
                          const int* __restrict__ context_lens, int num_rows, int page_size, int heads, int kv_heads,
-                         float scale_log2, int window, int keep_first) {
+                         float scale_log2, int window, int keep_first, AttentionExtras extras) {
   constexpr int STRIDE = D + 8;
   constexpr int TILE_ELEMS = kKeyTile * STRIDE;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -725,9 +730,22 @@ prefill_attention_kernel(const bf16* __restrict__ q, size_t q_stride, bf16* __re
   cp_async_wait<0>();
   l[0] = quad_sum(l[0]);
   l[1] = quad_sum(l[1]);
+  if (extras.sinks != nullptr) {                              // (a row without keys keeps l = 0)
+    if (l[0] > 0.0f) l[0] += sink_term(extras, head, m[0]);
+    if (l[1] > 0.0f) l[1] += sink_term(extras, head, m[1]);
+  }
   const float inv0 = l[0] > 0.0f ? 1.0f / l[0] : 0.0f, inv1 = l[1] > 0.0f ? 1.0f / l[1] : 0.0f;
-  bf16* out0 = out + ((size_t)(q_begin + local0 + local_r0) * heads + head) * D;
-  bf16* out1 = out + ((size_t)(q_begin + local0 + local_r1) * heads + head) * D;
+  const size_t token0 = (size_t)(q_begin + local0 + local_r0), token1 = (size_t)(q_begin + local0 + local_r1);
+  bf16* out0 = out + (token0 * heads + head) * D;
+  bf16* out1 = out + (token1 * heads + head) * D;
+  if (extras.gate != nullptr) {
+#pragma unroll
+    for (int nt = 0; nt < D / 8; ++nt) {
+      const size_t column = (size_t)head * D + nt * 8 + c;
+      if (valid0) { o[nt][0] *= gate_factor(extras, token0, column); o[nt][1] *= gate_factor(extras, token0, column + 1); }
+      if (valid1) { o[nt][2] *= gate_factor(extras, token1, column); o[nt][3] *= gate_factor(extras, token1, column + 1); }
+    }
+  }
 #pragma unroll
   for (int nt = 0; nt < D / 8; ++nt) {
     if (valid0) *reinterpret_cast<uint32_t*>(out0 + nt * 8 + c) = pack_bf16(o[nt][0] * inv0, o[nt][1] * inv0);
@@ -751,13 +769,13 @@ int set_smem(Kernel kernel, size_t bytes, const char* what, bool& done) {
 // The merge kernel for this many partitions.  (A window can only lower the number of partitions a row has.)
 template <int D>
 int launch_merge(const float* partial_o, const float* partial_ml, const int* positions, int rows, int heads, int window,
-                 int partition, int num_partitions, bf16* out, cudaStream_t stream) {
+                 int partition, int num_partitions, bf16* out, cudaStream_t stream, AttentionExtras extras = {}) {
   if (num_partitions <= kMergeFew)
     return mir_launch("decode_merge", decode_merge_few_kernel<D>, dim3((heads + kMergeWarps - 1) / kMergeWarps, rows),
                       dim3(kMergeWarps * 32), 0, stream, 0, partial_o, partial_ml, positions, heads, window, partition,
-                      num_partitions, out);
+                      num_partitions, out, extras);
   return mir_launch("decode_merge", decode_merge_kernel<D>, dim3(heads, rows), dim3(kMergeWarps * 32), 0, stream, 0,
-                    partial_o, partial_ml, positions, heads, window, partition, num_partitions, out);
+                    partial_o, partial_ml, positions, heads, window, partition, num_partitions, out, extras);
 }
 
 template <int D, int STAGES>
@@ -765,7 +783,7 @@ int launch_decode_staged(const bf16* q, size_t q_stride, bf16* out, const bf16* 
                          const int* block_table, int table_width, const int* positions, int rows, int page_size,
                          int heads, int kv_heads, float scale, int window, int partition, int num_partitions,
                          float* partial_o, float* partial_ml, cudaStream_t stream, int keep_first = 0,
-                         int* virtual_positions = nullptr) {
+                         int* virtual_positions = nullptr, AttentionExtras extras = {}) {
   const size_t pipeline = (size_t)kDecodeWarps * STAGES * 2 * kDecodeTile * (D + 8) * sizeof(bf16);
   const size_t combine = (size_t)kDecodeWarps * kDecodeHeads * (D + 2) * sizeof(float);
   const size_t smem = pipeline > combine ? pipeline : combine;
@@ -779,11 +797,13 @@ int launch_decode_staged(const bf16* q, size_t q_stride, bf16* out, const bf16* 
                            dim3(kDecodeWarps * 32), smem, stream, 0, q, q_stride, k_pages, v_pages, block_table,
                            table_width, positions, page_size, heads, kv_heads, scale * 1.4426950408889634f, window,
                            partition, num_partitions, rows <= 4 ? 1 : 0, partial_o, partial_ml, out, keep_first,
-                           virtual_positions);
+                           virtual_positions, extras);
   if (status != MIR_OK || num_partitions == 1) return status;
   if (keep_first > 0 && window > 0)      // the partitions were counted in the kernel's own numbering of the visible keys
-    return launch_merge<D>(partial_o, partial_ml, virtual_positions, rows, heads, 0, partition, num_partitions, out, stream);
-  return launch_merge<D>(partial_o, partial_ml, positions, rows, heads, window, partition, num_partitions, out, stream);
+    return launch_merge<D>(partial_o, partial_ml, virtual_positions, rows, heads, 0, partition, num_partitions, out, stream,
+                           extras);
+  return launch_merge<D>(partial_o, partial_ml, positions, rows, heads, window, partition, num_partitions, out, stream,
+                         extras);
 }
 
 long long g_deep_ring_ctas = 1536;                              // up to this many CTAs run three tiles in flight per warp
@@ -791,23 +811,24 @@ template <int D>
 int launch_decode(const bf16* q, size_t q_stride, bf16* out, const bf16* k_pages, const bf16* v_pages,
                   const int* block_table, int table_width, const int* positions, int rows, int page_size, int heads,
                   int kv_heads, float scale, int window, int partition, int num_partitions, float* partial_o,
-                  float* partial_ml, cudaStream_t stream, int keep_first = 0, int* virtual_positions = nullptr) {
+                  float* partial_ml, cudaStream_t stream, int keep_first = 0, int* virtual_positions = nullptr,
+                  AttentionExtras extras = {}) {
   const int group = heads / kv_heads;
   const long long ctas = (long long)num_partitions * kv_heads * ((group + kDecodeHeads - 1) / kDecodeHeads) * rows;
   if (ctas <= g_deep_ring_ctas)
     return launch_decode_staged<D, 3>(q, q_stride, out, k_pages, v_pages, block_table, table_width, positions, rows,
                                       page_size, heads, kv_heads, scale, window, partition, num_partitions, partial_o,
-                                      partial_ml, stream, keep_first, virtual_positions);
+                                      partial_ml, stream, keep_first, virtual_positions, extras);
   return launch_decode_staged<D, 2>(q, q_stride, out, k_pages, v_pages, block_table, table_width, positions, rows,
                                     page_size, heads, kv_heads, scale, window, partition, num_partitions, partial_o,
-                                    partial_ml, stream, keep_first, virtual_positions);
+                                    partial_ml, stream, keep_first, virtual_positions, extras);
 }
 
 template <int D>
 int launch_prefill(const bf16* q, size_t q_stride, bf16* out, const bf16* k_pages, const bf16* v_pages,
                    const int* block_table, int table_width, const int* query_starts, const int* context_lens,
                    int num_rows, int tokens, int page_size, int heads, int kv_heads, float scale, int window,
-                   int keep_first, cudaStream_t stream) {
+                   int keep_first, cudaStream_t stream, AttentionExtras extras = {}) {
   const size_t smem = (size_t)2 * 2 * kKeyTile * (D + 8) * sizeof(bf16);
   static bool smem_set = false;
   int status = set_smem(prefill_attention_kernel<D>, smem, "prefill_attention", smem_set);
@@ -820,7 +841,7 @@ int launch_prefill(const bf16* q, size_t q_stride, bf16* out, const bf16* k_page
   return mir_launch("prefill_attention", prefill_attention_kernel<D>, dim3(heads, tiles), dim3(kPrefillWarps * 32),
                     smem, stream, 0, q, q_stride, out, k_pages, v_pages, block_table, table_width, query_starts,
                     context_lens, num_rows, page_size, heads, kv_heads, scale * 1.4426950408889634f, window,
-                    keep_first);
+                    keep_first, extras);
 }
 
 bool bad_common(const char* what, int heads, int kv_heads, int head_dim, int page_size, int table_width, int window) {
@@ -853,9 +874,11 @@ MIR_EXPORT long long mir_decode_attention_scratch_floats(int rows, int heads, in
 
 // The merge of the partitions' results alone (the tcgen05 decode kernel leaves them in the same layout): scratch as
 // mir_decode_attention_bf16 lays it out, partial outputs then (maximum, denominator) pairs.
-MIR_EXPORT int mir_decode_merge_bf16(const float* partial_o, const float* partial_ml, const int* positions, int rows,
-                                     int heads, int head_dim, int window, int partition, int num_partitions, void* out,
-                                     cudaStream_t stream) {
+MIR_EXPORT int mir_decode_merge_extra_bf16(const float* partial_o, const float* partial_ml, const int* positions,
+                                           int rows, int heads, int head_dim, int window, int partition,
+                                           int num_partitions, void* out, cudaStream_t stream, const float* sinks,
+                                           const void* gate, long long gate_stride) {
+  const AttentionExtras extras{sinks, (const bf16*)gate, gate_stride};
   if (rows <= 0 || rows > 65535 || heads <= 0 || partition <= 0 || num_partitions <= 0 || window < 0 ||
       (head_dim != 64 && head_dim != 128) || partial_o == nullptr || partial_ml == nullptr) {
     mir_set_error("decode_merge: bad sizes (rows %d, heads %d, head_dim %d, partition %d, partitions %d)", rows, heads,
@@ -864,9 +887,16 @@ MIR_EXPORT int mir_decode_merge_bf16(const float* partial_o, const float* partia
   }
   if (head_dim == 64)
     return launch_merge<64>(partial_o, partial_ml, positions, rows, heads, window, partition, num_partitions, (bf16*)out,
-                            stream);
+                            stream, extras);
   return launch_merge<128>(partial_o, partial_ml, positions, rows, heads, window, partition, num_partitions, (bf16*)out,
-                           stream);
+                           stream, extras);
+}
+
+MIR_EXPORT int mir_decode_merge_bf16(const float* partial_o, const float* partial_ml, const int* positions, int rows,
+                                     int heads, int head_dim, int window, int partition, int num_partitions, void* out,
+                                     cudaStream_t stream) {
+  return mir_decode_merge_extra_bf16(partial_o, partial_ml, positions, rows, heads, head_dim, window, partition,
+                                     num_partitions, out, stream, nullptr, nullptr, 0);
 }
 
 // One token per row.  `partition` (a multiple of 64) is how many keys one CTA takes; num_partitions must be
@@ -899,13 +929,18 @@ MIR_EXPORT int mir_decode_attention_bf16(const void* q, long long q_stride, void
                             partition, num_partitions, partial_o, partial_ml, stream);
 }
 
-// The same with a window's kept first keys (keep_first; virtual_positions: rows ints of scratch for the merge).
-MIR_EXPORT int mir_decode_attention_kept_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
-                                         const void* v_pages, const int* block_table, int table_width,
-                                         const int* positions, int rows, int page_size, int heads, int kv_heads,
-                                         int head_dim, float scale, int window, int partition, int num_partitions,
-                                         float* scratch, long long scratch_floats, cudaStream_t stream, int keep_first, int* virtual_positions) {
+// The same with a window's kept first keys (keep_first; virtual_positions: rows ints of scratch for the merge), and
+// with what AttentionExtras describes: sinks [heads] 32-bit or null; gate rows [token][heads * head_dim] with a row
+// stride in elements, or null.
+MIR_EXPORT int mir_decode_attention_extra_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                               const void* v_pages, const int* block_table, int table_width,
+                                               const int* positions, int rows, int page_size, int heads, int kv_heads,
+                                               int head_dim, float scale, int window, int partition,
+                                               int num_partitions, float* scratch, long long scratch_floats,
+                                               cudaStream_t stream, int keep_first, int* virtual_positions,
+                                               const float* sinks, const void* gate, long long gate_stride) {
   if (rows == 0) return MIR_OK;
+  const AttentionExtras extras{sinks, (const bf16*)gate, gate_stride};
   if (keep_first < 0 || (keep_first > 0 && window > 0 && virtual_positions == nullptr)) {
     mir_set_error("decode_attention: kept first keys need room for one number per row");
     return MIR_BAD_ARGUMENT;
@@ -926,21 +961,39 @@ MIR_EXPORT int mir_decode_attention_kept_bf16(const void* q, long long q_stride,
   if (head_dim == 64)
     return launch_decode<64>((const bf16*)q, (size_t)q_stride, (bf16*)out, (const bf16*)k_pages, (const bf16*)v_pages,
                              block_table, table_width, positions, rows, page_size, heads, kv_heads, scale, window,
-                             partition, num_partitions, partial_o, partial_ml, stream, keep_first, virtual_positions);
+                             partition, num_partitions, partial_o, partial_ml, stream, keep_first, virtual_positions,
+                             extras);
   return launch_decode<128>((const bf16*)q, (size_t)q_stride, (bf16*)out, (const bf16*)k_pages, (const bf16*)v_pages,
                             block_table, table_width, positions, rows, page_size, heads, kv_heads, scale, window,
-                            partition, num_partitions, partial_o, partial_ml, stream, keep_first, virtual_positions);
+                            partition, num_partitions, partial_o, partial_ml, stream, keep_first, virtual_positions,
+                            extras);
+}
+
+MIR_EXPORT int mir_decode_attention_kept_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                              const void* v_pages, const int* block_table, int table_width,
+                                              const int* positions, int rows, int page_size, int heads, int kv_heads,
+                                              int head_dim, float scale, int window, int partition, int num_partitions,
+                                              float* scratch, long long scratch_floats, cudaStream_t stream,
+                                              int keep_first, int* virtual_positions) {
+  return mir_decode_attention_extra_bf16(q, q_stride, out, k_pages, v_pages, block_table, table_width, positions, rows,
+                                         page_size, heads, kv_heads, head_dim, scale, window, partition, num_partitions,
+                                         scratch, scratch_floats, stream, keep_first, virtual_positions, nullptr,
+                                         nullptr, 0);
 }
 
 // Any mix of portions: row r has tokens query_starts[r] .. query_starts[r+1]-1 of the packed batch, and its
 // request holds context_lens[r] tokens after this step (so the portion starts at context_lens[r] - count).
 // keep_first: with a window, the first keys of every request that stay visible to all its later queries.
-MIR_EXPORT int mir_prefill_attention_kept_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
-                                               const void* v_pages, const int* block_table, int table_width,
-                                               const int* query_starts, const int* context_lens, int num_rows,
-                                               int tokens, int page_size, int heads, int kv_heads, int head_dim,
-                                               float scale, int window, int keep_first, cudaStream_t stream) {
+// sinks, gate, gate_stride: what AttentionExtras describes (null for none); gate rows are indexed by the token's place
+// in the packed batch.
+MIR_EXPORT int mir_prefill_attention_extra_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                                const void* v_pages, const int* block_table, int table_width,
+                                                const int* query_starts, const int* context_lens, int num_rows,
+                                                int tokens, int page_size, int heads, int kv_heads, int head_dim,
+                                                float scale, int window, int keep_first, cudaStream_t stream,
+                                                const float* sinks, const void* gate, long long gate_stride) {
   if (tokens == 0 || num_rows == 0) return MIR_OK;
+  const AttentionExtras extras{sinks, (const bf16*)gate, gate_stride};
   if (bad_common("prefill_attention", heads, kv_heads, head_dim, page_size, table_width, window) || keep_first < 0)
     return MIR_BAD_ARGUMENT;
   if (tokens < 0 || num_rows < 0) {
@@ -950,10 +1003,20 @@ MIR_EXPORT int mir_prefill_attention_kept_bf16(const void* q, long long q_stride
   if (head_dim == 64)
     return launch_prefill<64>((const bf16*)q, (size_t)q_stride, (bf16*)out, (const bf16*)k_pages, (const bf16*)v_pages,
                               block_table, table_width, query_starts, context_lens, num_rows, tokens, page_size, heads,
-                              kv_heads, scale, window, keep_first, stream);
+                              kv_heads, scale, window, keep_first, stream, extras);
   return launch_prefill<128>((const bf16*)q, (size_t)q_stride, (bf16*)out, (const bf16*)k_pages, (const bf16*)v_pages,
                              block_table, table_width, query_starts, context_lens, num_rows, tokens, page_size, heads,
-                             kv_heads, scale, window, keep_first, stream);
+                             kv_heads, scale, window, keep_first, stream, extras);
+}
+
+MIR_EXPORT int mir_prefill_attention_kept_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                               const void* v_pages, const int* block_table, int table_width,
+                                               const int* query_starts, const int* context_lens, int num_rows,
+                                               int tokens, int page_size, int heads, int kv_heads, int head_dim,
+                                               float scale, int window, int keep_first, cudaStream_t stream) {
+  return mir_prefill_attention_extra_bf16(q, q_stride, out, k_pages, v_pages, block_table, table_width, query_starts,
+                                          context_lens, num_rows, tokens, page_size, heads, kv_heads, head_dim, scale,
+                                          window, keep_first, stream, nullptr, nullptr, 0);
 }
 
 MIR_EXPORT int mir_prefill_attention_bf16(const void* q, long long q_stride, void* out, const void* k_pages,

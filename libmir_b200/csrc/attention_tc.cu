@@ -292,7 +292,7 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                             const __grid_constant__ CUtensorMap v_tile_map, bf16* __restrict__ out,
                             const int* __restrict__ block_table, int table_width, const int* __restrict__ query_starts,
                             const int* __restrict__ context_lens, int num_rows, int page_size, int heads, int kv_heads,
-                            float scale_log2, int window, int tile_slots, int keep_first) {
+                            float scale_log2, int window, int tile_slots, int keep_first, AttentionExtras extras) {
   constexpr int kThreads = threads_for(kStreams);
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long barriers[BARRIERS];
@@ -637,6 +637,7 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         weight[other] = theirs > -INFINITY ? fast_exp2(theirs - top) : 0.0f;
         total += (denominators[slot][other][0][r] + denominators[slot][other][1][r]) * weight[other];
       }
+      if (total > 0.0f) total += sink_term(extras, w.head, top);   // a sink: one more term of the denominator
       // the item's last product is over
       if (alive && !wait_barrier(bar(ITEM_DONE), (uint32_t)n & 1u)) {
         g_tc_attention_error = 3;
@@ -676,6 +677,18 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             tensor_fence_before_sync();
             barrier_arrive(bar(O_FREE));
             ATT_STAMP(stamp_item, 3);
+          }
+          if (valid_row && alive && extras.gate != nullptr) {
+            // the gate's 32 elements of this token and head (16-byte pieces: the entry point checks the alignment)
+            const bf16* gate = extras.gate + (size_t)(w.q_row0 + r) * (size_t)extras.gate_stride +
+                               (size_t)w.head * kDim + column + c0;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              float g[8];
+              load8(gate + i, g);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) o[i + j] *= 1.0f / (1.0f + __expf(-g[j]));
+            }
           }
           if (valid_row && alive) {
 #pragma unroll
@@ -734,13 +747,20 @@ MIR_EXPORT int mir_prefill_attention_tc_takes(int head_dim, int page_size) {
 // heads * 128 columns are the rotated queries; out is [tokens, heads * 128]; k_pages and v_pages are
 // [cache_rows, kv_heads, 128].
 // keep_first: with a window, the first keys of every request that stay visible to all its later queries.
-MIR_EXPORT int mir_prefill_attention_tc_kept_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
-                                                  const void* v_pages, long long cache_rows, const int* block_table,
-                                                  int table_width, const int* query_starts, const int* context_lens,
-                                                  int num_rows, int tokens, int page_size, int heads, int kv_heads,
-                                                  int head_dim, float scale, int window, int keep_first,
-                                                  cudaStream_t stream) {
+// sinks, gate, gate_stride: what AttentionExtras describes (null for none); the gate's rows are read in 16-byte pieces.
+MIR_EXPORT int mir_prefill_attention_tc_extra_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                                   const void* v_pages, long long cache_rows, const int* block_table,
+                                                   int table_width, const int* query_starts, const int* context_lens,
+                                                   int num_rows, int tokens, int page_size, int heads, int kv_heads,
+                                                   int head_dim, float scale, int window, int keep_first,
+                                                   cudaStream_t stream, const float* sinks, const void* gate,
+                                                   long long gate_stride) {
   if (num_rows == 0 || tokens == 0) return MIR_OK;
+  if (gate != nullptr && (((uintptr_t)gate & 15) || (gate_stride % 8))) {
+    mir_set_error("prefill_attention_tc: the gate's rows must be 16-byte aligned");
+    return MIR_BAD_ARGUMENT;
+  }
+  const AttentionExtras extras{sinks, (const bf16*)gate, gate_stride};
   if (keep_first < 0) { mir_set_error("prefill_attention_tc: keep_first is negative"); return MIR_BAD_ARGUMENT; }
   if (!mir_prefill_attention_tc_takes(head_dim, page_size) || heads <= 0 || kv_heads <= 0 || heads % kv_heads ||
       table_width <= 0 || window < 0 || num_rows < 0 || tokens < 0 || scale <= 0.0f ||
@@ -797,16 +817,27 @@ MIR_EXPORT int mir_prefill_attention_tc_kept_bf16(const void* q, long long q_str
     return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel<2, true>, dim3(ctas), dim3(threads_for(2)),
                       (size_t)kSmemBytes, stream, 0, q_map, k_map, v_map, k_tile_map, v_tile_map, (bf16*)out, block_table, table_width,
                       query_starts, context_lens, num_rows, page_size, heads, kv_heads,
-                      scale * 1.4426950408889634f, window, tile_slots, window > 0 ? keep_first : 0);
+                      scale * 1.4426950408889634f, window, tile_slots, window > 0 ? keep_first : 0, extras);
   if (g_streams == 2)
     return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel<2, false>, dim3(ctas), dim3(threads_for(2)),
                       (size_t)kSmemBytes, stream, 0, q_map, k_map, v_map, k_tile_map, v_tile_map, (bf16*)out, block_table, table_width,
                       query_starts, context_lens, num_rows, page_size, heads, kv_heads,
-                      scale * 1.4426950408889634f, window, tile_slots, window > 0 ? keep_first : 0);
+                      scale * 1.4426950408889634f, window, tile_slots, window > 0 ? keep_first : 0, extras);
   return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel<1, false>, dim3(ctas), dim3(threads_for(1)),
                     (size_t)kSmemBytes, stream, 0, q_map, k_map, v_map, k_tile_map, v_tile_map, (bf16*)out, block_table, table_width,
                     query_starts, context_lens, num_rows, page_size, heads, kv_heads,
-                    scale * 1.4426950408889634f, window, tile_slots, window > 0 ? keep_first : 0);
+                    scale * 1.4426950408889634f, window, tile_slots, window > 0 ? keep_first : 0, extras);
+}
+
+MIR_EXPORT int mir_prefill_attention_tc_kept_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                                  const void* v_pages, long long cache_rows, const int* block_table,
+                                                  int table_width, const int* query_starts, const int* context_lens,
+                                                  int num_rows, int tokens, int page_size, int heads, int kv_heads,
+                                                  int head_dim, float scale, int window, int keep_first,
+                                                  cudaStream_t stream) {
+  return mir_prefill_attention_tc_extra_bf16(q, q_stride, out, k_pages, v_pages, cache_rows, block_table, table_width,
+                                             query_starts, context_lens, num_rows, tokens, page_size, heads, kv_heads,
+                                             head_dim, scale, window, keep_first, stream, nullptr, nullptr, 0);
 }
 
 MIR_EXPORT int mir_prefill_attention_tc_bf16(const void* q, long long q_stride, void* out, const void* k_pages,

@@ -133,7 +133,8 @@ tc_decode_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __gr
                            const bf16* __restrict__ q, size_t q_stride, const int* __restrict__ block_table,
                            int table_width, const int* __restrict__ positions, int page_size, int heads, int kv_heads,
                            float scale_log2, int window, int partition, int num_partitions, int part_slow,
-                           float* __restrict__ partial_o, float* __restrict__ partial_ml, bf16* __restrict__ out) {
+                           float* __restrict__ partial_o, float* __restrict__ partial_ml, bf16* __restrict__ out,
+                           AttentionExtras extras) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long barriers[BARRIERS];
   __shared__ uint32_t tmem_base_slot;
@@ -377,10 +378,12 @@ tc_decode_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __gr
 #pragma unroll
       for (int g = 0; g < G; ++g) {
         if (g >= valid_heads) break;
-        const float denom = (sums[0][g] + sums[1][g]) + (sums[2][g] + sums[3][g]);
+        float denom = (sums[0][g] + sums[1][g]) + (sums[2][g] + sums[3][g]);
         const size_t head = (size_t)row * heads + head0 + g;
         if (num_partitions == 1) {
-          out[head * kDim + r] = __float2bfloat16_rn(denom > 0.0f ? o[g] / denom : 0.0f);
+          if (denom > 0.0f) denom += sink_term(extras, head0 + g, reference[g]);
+          out[head * kDim + r] = __float2bfloat16_rn(
+              denom > 0.0f ? o[g] / denom * gate_factor(extras, row, (size_t)(head0 + g) * kDim + r) : 0.0f);
         } else {
           partial_o[(head * num_partitions + part) * kDim + r] = denom > 0.0f ? o[g] : 0.0f;
           if (r == 0) {
@@ -406,7 +409,7 @@ int launch(const CUtensorMap& k_map, const CUtensorMap& v_map, const CUtensorMap
            const CUtensorMap& v_tile_map, const bf16* q, size_t q_stride, const int* block_table,
            int table_width, const int* positions, int rows, int page_size, int heads, int kv_heads, float scale,
            int window, int partition, int num_partitions, float* partial_o, float* partial_ml, bf16* out,
-           cudaStream_t stream) {
+           cudaStream_t stream, AttentionExtras extras) {
   static bool configured = false;
   if (!configured) {
     const cudaError_t err = cudaFuncSetAttribute(tc_decode_attention_kernel<G>,
@@ -427,7 +430,7 @@ int launch(const CUtensorMap& k_map, const CUtensorMap& v_map, const CUtensorMap
                          dim3(kThreads), (size_t)kSmemBytes, stream, 0, k_map, v_map, k_tile_map, v_tile_map, q, q_stride,
                          block_table,
                          table_width, positions, page_size, heads, kv_heads, scale * 1.4426950408889634f, window,
-                         partition, num_partitions, rows <= 4 ? 1 : 0, partial_o, partial_ml, out);
+                         partition, num_partitions, rows <= 4 ? 1 : 0, partial_o, partial_ml, out, extras);
 }
 
 }  // namespace
@@ -447,14 +450,17 @@ MIR_EXPORT int mir_decode_attention_tc_takes(int head_dim, int page_size, int pa
          page_size % 8 == 0 && partition > 0 && partition % kKeys == 0;
 }
 
-// One token per row, as mir_decode_attention_bf16; k_pages and v_pages are [cache_rows, kv_heads, 128].
-MIR_EXPORT int mir_decode_attention_tc_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
-                                            const void* v_pages, long long cache_rows, const int* block_table,
-                                            int table_width, const int* positions, int rows, int page_size, int heads,
-                                            int kv_heads, int head_dim, float scale, int window, int partition,
-                                            int num_partitions, float* scratch, long long scratch_floats,
-                                            cudaStream_t stream) {
+// One token per row, as mir_decode_attention_bf16; k_pages and v_pages are [cache_rows, kv_heads, 128].  sinks, gate,
+// gate_stride: what AttentionExtras describes (null for none).
+MIR_EXPORT int mir_decode_attention_tc_extra_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                                  const void* v_pages, long long cache_rows, const int* block_table,
+                                                  int table_width, const int* positions, int rows, int page_size,
+                                                  int heads, int kv_heads, int head_dim, float scale, int window,
+                                                  int partition, int num_partitions, float* scratch,
+                                                  long long scratch_floats, cudaStream_t stream, const float* sinks,
+                                                  const void* gate, long long gate_stride) {
   if (rows == 0) return MIR_OK;
+  const AttentionExtras extras{sinks, (const bf16*)gate, gate_stride};
   if (!mir_decode_attention_tc_takes(head_dim, page_size, partition) || heads <= 0 || kv_heads <= 0 ||
       heads % kv_heads || table_width <= 0 || window < 0 || rows < 0 || rows > 65535 || num_partitions <= 0 ||
       num_partitions > 65535 || (q_stride % 8) || q_stride < (long long)heads * kDim || ((uintptr_t)q & 15) ||
@@ -486,10 +492,22 @@ MIR_EXPORT int mir_decode_attention_tc_bf16(const void* q, long long q_stride, v
   float* partial_ml = scratch ? scratch + (size_t)rows * heads * num_partitions * head_dim : nullptr;
 #define MIR_SPLIT(G)                                                                                                 \
   launch<G>(k_map, v_map, k_tile_map, v_tile_map, (const bf16*)q, (size_t)q_stride, block_table, table_width, positions, rows, page_size, heads, \
-            kv_heads, scale, window, partition, num_partitions, partial_o, partial_ml, (bf16*)out, stream)
+            kv_heads, scale, window, partition, num_partitions, partial_o, partial_ml, (bf16*)out, stream, extras)
   status = columns <= 4 ? MIR_SPLIT(4) : (columns <= 8 ? MIR_SPLIT(8) : MIR_SPLIT(16));
 #undef MIR_SPLIT
   if (status != MIR_OK || num_partitions == 1) return status;
-  return mir_decode_merge_bf16(partial_o, partial_ml, positions, rows, heads, head_dim, window, partition,
-                               num_partitions, out, stream);
+  return mir_decode_merge_extra_bf16(partial_o, partial_ml, positions, rows, heads, head_dim, window, partition,
+                                     num_partitions, out, stream, sinks, gate, gate_stride);
+}
+
+MIR_EXPORT int mir_decode_attention_tc_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                            const void* v_pages, long long cache_rows, const int* block_table,
+                                            int table_width, const int* positions, int rows, int page_size, int heads,
+                                            int kv_heads, int head_dim, float scale, int window, int partition,
+                                            int num_partitions, float* scratch, long long scratch_floats,
+                                            cudaStream_t stream) {
+  return mir_decode_attention_tc_extra_bf16(q, q_stride, out, k_pages, v_pages, cache_rows, block_table, table_width,
+                                            positions, rows, page_size, heads, kv_heads, head_dim, scale, window,
+                                            partition, num_partitions, scratch, scratch_floats, stream, nullptr,
+                                            nullptr, 0);
 }

@@ -111,6 +111,23 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&out)[8]) {
   }
 }
 
+// What softmax attention may do beyond keys and values.  sinks: one 32-bit number per query head whose exponential
+// joins the softmax's denominator (no key, no value, not scaled).  gate: rows [token, heads * head_dim] with a row
+// stride of their own; a head's result is multiplied by the sigmoid of its gate elements before it is stored.
+struct AttentionExtras {
+  const float* sinks = nullptr;
+  const __nv_bfloat16* gate = nullptr;
+  long long gate_stride = 0;
+};
+// The sink's share of a denominator whose terms are exp2(score * log2 e - reference).
+__device__ __forceinline__ float sink_term(const AttentionExtras& extras, int head, float reference) {
+  return extras.sinks != nullptr ? exp2f(extras.sinks[head] * 1.4426950408889634f - reference) : 0.0f;
+}
+__device__ __forceinline__ float gate_factor(const AttentionExtras& extras, size_t token, size_t column) {
+  if (extras.gate == nullptr) return 1.0f;
+  return 1.0f / (1.0f + __expf(-__bfloat162float(extras.gate[token * (size_t)extras.gate_stride + column])));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

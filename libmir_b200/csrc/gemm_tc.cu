@@ -51,8 +51,9 @@ constexpr int kStageStride = (kTileM + 256) * 128;   // 48 KB: 128 token rows an
 constexpr int kEpilogueWarps = 8;          // two per quarter of the accumulator lanes; they share its columns
 constexpr int kThreads = (2 + kEpilogueWarps) * 32;  // producer warp, issuer warp, epilogue warps
 constexpr uint32_t kTmemColumns = 512;      // two accumulators of up to 256 columns
-// GELU: STORE of gelu_tanh(acc), no bias; GELU_ERF: the same with the exact form 0.5 z (1 + erf(z / sqrt 2))
-enum Epilogue : int { STORE = 0, ACCUM = 1, F32 = 2, SWIGLU = 3, GELU = 4, GELU_ERF = 5 };
+// GELU: STORE of gelu_tanh(acc), no bias; GELU_ERF: the same with the exact form 0.5 z (1 + erf(z / sqrt 2)); RELU2: the
+// same with the square of relu
+enum Epilogue : int { STORE = 0, ACCUM = 1, F32 = 2, SWIGLU = 3, GELU = 4, GELU_ERF = 5, RELU2 = 6 };
 
 __device__ int g_tc_gemm_error = 0;
 
@@ -230,10 +231,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0.5f * v[i] * (1.0f + erff(v[i] * 0.70710678118654752f));
         }
+        if (MODE == RELU2) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) { const float positive = fmaxf(v[i], 0.0f); v[i] = positive * positive; }
+        }
         if (c0 + 64 >= out_width) release();                 // the last columns are in registers
         const int limit = min(n, n0 + out_width);            // columns of this tile that exist
         if (source_row < row_end) {
-          if (MODE == STORE || MODE == SWIGLU || MODE == GELU || MODE == GELU_ERF) {
+          if (MODE == STORE || MODE == SWIGLU || MODE == GELU || MODE == GELU_ERF || MODE == RELU2) {
             bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)row * ldo + n0 + c0;
             if (n0 + c0 + 32 <= limit && (ldo % 8) == 0) {
 #pragma unroll
@@ -423,7 +428,8 @@ MIR_EXPORT int mir_gemm_tc_set_width(int width) {
   return MIR_OK;
 }
 
-// mode: 0 store bf16, 1 accumulate into float, 2 float, 4 store bf16 of the tanh GELU, 5 of the exact GELU, 3 SwiGLU (w = [gate; up],
+// mode: 0 store bf16, 1 accumulate into float, 2 float, 4 store bf16 of the tanh GELU, 5 of the exact GELU, 6 of the
+// square of relu, 3 SwiGLU (w = [gate; up],
 // up rows start at up_offset, n = number of output columns).  k and ldx must be multiples of 8, x and w 16-byte
 // aligned; m, n, k need not be multiples of the tile sizes.
 MIR_EXPORT int mir_gemm_tc_bf16(int mode, const void* x, int ldx, const void* w, const void* bias, void* out, int ldo,
@@ -448,6 +454,9 @@ MIR_EXPORT int mir_gemm_tc_bf16(int mode, const void* x, int ldx, const void* w,
     case GELU_ERF:
       if (bias) { mir_set_error("tc_gemm: the GELU epilogue takes no bias"); return MIR_BAD_ARGUMENT; }
       return launch<GELU_ERF>(x, ldx, w, nullptr, out, ldo, m, n, k, 0, stream);
+    case RELU2:
+      if (bias) { mir_set_error("tc_gemm: the squared-relu epilogue takes no bias"); return MIR_BAD_ARGUMENT; }
+      return launch<RELU2>(x, ldx, w, nullptr, out, ldo, m, n, k, 0, stream);
   }
   mir_set_error("tc_gemm: unknown mode %d", mode);
   return MIR_BAD_ARGUMENT;

@@ -60,7 +60,7 @@ struct StreamNorm {
   float* best_value;         // float32 epilogue (the output head): [m][best_stride] the largest finite result of every
   int* best_index;           //   32 columns (entry 4 x tile + warp) and its column, ties to the lower column; or null
   int best_stride;
-  int activation;            // store epilogue: 0 none, 1 the tanh GELU of the result, 2 the exact (erf) GELU
+  int activation;            // store epilogue: 0 none, 1 the tanh GELU of the result, 2 the exact (erf) GELU, 3 relu squared
 };
 
 // (Shared memory lets three CTAs share an SM; the registers are capped as if six did: 56 instead of up to 95 per
@@ -316,6 +316,8 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
                 stored = 0.5f * result * (1.0f + t);
               } else if (norm.activation == 2) {              // 0.5 z (1 + erf(z / sqrt 2))
                 stored = 0.5f * result * (1.0f + erff(result * 0.70710678118654752f));
+              } else if (norm.activation == 3) {              // the square of relu
+                stored = fmaxf(result, 0.0f) * fmaxf(result, 0.0f);
               }
               reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] = __float2bfloat16_rn(stored);
             } else {
@@ -448,10 +450,10 @@ MIR_EXPORT int mir_gemm_tc_stream_bf16(int mode, const void* x, int ldx, const v
                                        int sumsq_tiles, float eps, float* sumsq_out, const float* next_weight,
                                        void* weighted_out, int ld_weighted, cudaStream_t stream) {
   if (m == 0 || n == 0) return MIR_OK;
-  const bool gelu = mode == 4 || mode == 5;                    // modes 4, 5: the store epilogue with the tanh / exact GELU, no bias
-  const int activation = mode == 4 ? 1 : (mode == 5 ? 2 : 0);
+  const bool gelu = mode == 4 || mode == 5 || mode == 6;       // the store epilogue with the tanh / exact GELU or relu squared, no bias
+  const int activation = mode == 4 ? 1 : (mode == 5 ? 2 : (mode == 6 ? 3 : 0));
   if (gelu) {
-    if (bias) { mir_set_error("tc_stream: the GELU epilogue takes no bias"); return MIR_BAD_ARGUMENT; }
+    if (bias) { mir_set_error("tc_stream: an activation epilogue takes no bias"); return MIR_BAD_ARGUMENT; }
     mode = STORE;
   }
   if (m < 0 || m > 128 || n < 0 || k <= 0 || (k % 8) || ldo < n || ((uintptr_t)w & 15) || (ldx % 8) || ldx < k ||

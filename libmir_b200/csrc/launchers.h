@@ -45,6 +45,23 @@ int mir_decode_attention_bf16(const void* q, long long q_stride, void* out, cons
                               int num_partitions, float* scratch, long long scratch_floats, cudaStream_t stream);
 int mir_decode_merge_bf16(const float* partial_o, const float* partial_ml, const int* positions, int rows, int heads,
                           int head_dim, int window, int partition, int num_partitions, void* out, cudaStream_t stream);
+int mir_decode_merge_extra_bf16(const float* partial_o, const float* partial_ml, const int* positions, int rows,
+                                int heads, int head_dim, int window, int partition, int num_partitions, void* out,
+                                cudaStream_t stream, const float* sinks, const void* gate, long long gate_stride);
+int mir_decode_attention_extra_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                    const void* v_pages, const int* block_table, int table_width, const int* positions,
+                                    int rows, int page_size, int heads, int kv_heads, int head_dim, float scale,
+                                    int window, int partition, int num_partitions, float* scratch,
+                                    long long scratch_floats, cudaStream_t stream, int keep_first,
+                                    int* virtual_positions, const float* sinks, const void* gate,
+                                    long long gate_stride);
+int mir_decode_attention_tc_extra_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                       const void* v_pages, long long cache_rows, const int* block_table,
+                                       int table_width, const int* positions, int rows, int page_size, int heads,
+                                       int kv_heads, int head_dim, float scale, int window, int partition,
+                                       int num_partitions, float* scratch, long long scratch_floats,
+                                       cudaStream_t stream, const float* sinks, const void* gate,
+                                       long long gate_stride);
 int mir_decode_attention_tc_takes(int head_dim, int page_size, int partition);
 int mir_decode_attention_tc_bf16(const void* q, long long q_stride, void* out, const void* k_pages, const void* v_pages,
                                  long long cache_rows, const int* block_table, int table_width, const int* positions,

@@ -147,19 +147,35 @@ MIR_EXPORT int mir_decode_partition_keys(int rows, int heads, int kv_heads, int 
 
 // Attention of single decoded tokens over the pages: the tcgen05 kernel where it takes the sizes, else the mma.sync
 // kernel.  Arguments as mir_decode_attention_bf16, and how many token rows the cache tensors have.
+// sinks (32-bit, one per query head: its exponential joins the softmax's denominator) and gate (rows [token][heads *
+// head_dim] with a row stride in elements: the result is multiplied by its sigmoid) may be null.
+MIR_EXPORT int mir_decode_attention_paged_extra_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                                     const void* v_pages, long long cache_rows, const int* block_table,
+                                                     int table_width, const int* positions, int rows, int page_size,
+                                                     int heads, int kv_heads, int head_dim, float scale, int window,
+                                                     int partition, int num_partitions, float* scratch,
+                                                     long long scratch_floats, cudaStream_t stream, const float* sinks,
+                                                     const void* gate, long long gate_stride) {
+  if (g_decode_tensor_cores && cache_rows > 0 && mir_decode_attention_tc_takes(head_dim, page_size, partition))
+    return mir_decode_attention_tc_extra_bf16(q, q_stride, out, k_pages, v_pages, cache_rows, block_table, table_width,
+                                              positions, rows, page_size, heads, kv_heads, head_dim, scale, window,
+                                              partition, num_partitions, scratch, scratch_floats, stream, sinks, gate,
+                                              gate_stride);
+  return mir_decode_attention_extra_bf16(q, q_stride, out, k_pages, v_pages, block_table, table_width, positions, rows,
+                                         page_size, heads, kv_heads, head_dim, scale, window, partition, num_partitions,
+                                         scratch, scratch_floats, stream, 0, nullptr, sinks, gate, gate_stride);
+}
+
 MIR_EXPORT int mir_decode_attention_paged_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
                                                const void* v_pages, long long cache_rows, const int* block_table,
                                                int table_width, const int* positions, int rows, int page_size,
                                                int heads, int kv_heads, int head_dim, float scale, int window,
                                                int partition, int num_partitions, float* scratch,
                                                long long scratch_floats, cudaStream_t stream) {
-  if (g_decode_tensor_cores && cache_rows > 0 && mir_decode_attention_tc_takes(head_dim, page_size, partition))
-    return mir_decode_attention_tc_bf16(q, q_stride, out, k_pages, v_pages, cache_rows, block_table, table_width,
-                                        positions, rows, page_size, heads, kv_heads, head_dim, scale, window, partition,
-                                        num_partitions, scratch, scratch_floats, stream);
-  return mir_decode_attention_bf16(q, q_stride, out, k_pages, v_pages, block_table, table_width, positions, rows,
-                                   page_size, heads, kv_heads, head_dim, scale, window, partition, num_partitions,
-                                   scratch, scratch_floats, stream);
+  return mir_decode_attention_paged_extra_bf16(q, q_stride, out, k_pages, v_pages, cache_rows, block_table, table_width,
+                                               positions, rows, page_size, heads, kv_heads, head_dim, scale, window,
+                                               partition, num_partitions, scratch, scratch_floats, stream, nullptr,
+                                               nullptr, 0);
 }
 
 // What a caller has to provide for the attention of `rows` single tokens whose longest context (or block-table width)

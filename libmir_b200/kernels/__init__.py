@@ -92,6 +92,19 @@ _SIGNATURES = {
         "mir_decode_attention_kept_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                            c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p,
                                            c_longlong, c_void_p, c_int, c_void_p],
+        "mir_decode_attention_extra_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                            c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p,
+                                            c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong],
+        "mir_decode_attention_paged_extra_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong,
+                                                  c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                                  c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p,
+                                                  c_void_p, c_longlong],
+        "mir_prefill_attention_extra_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                             c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong],
+        "mir_prefill_attention_tc_extra_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
+                                                c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong],
         "mir_decode_attention_paged_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
                                             c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                                             c_int, c_void_p, c_longlong, c_void_p],
@@ -1075,6 +1088,13 @@ def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch
         head_dim if values_in_keys else 0, _ptr(sinks), _ptr(gate), gate.stride(0) if gate is not None else 0, _stream()))
 
 
+def _check_extras(what: str, sinks, gate, out: torch.Tensor, heads: int) -> None:
+    _require(sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == heads and sinks.is_contiguous()),
+             f"{what}: sinks are float32 [heads]")
+    _require(gate is None or (gate.dtype == out.dtype and gate.shape == out.shape and gate.stride(1) == 1),
+             f"{what}: the gate has out's shape and dtype")
+
+
 FAST_HEAD_DIMS = (64, 128)      # what the tensor-core attention kernels take; other sizes use the reference kernel
 
 
@@ -1108,12 +1128,17 @@ def decode_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor
                      block_table: torch.Tensor, positions: torch.Tensor, page_size: int, heads: int, kv_heads: int,
                      head_dim: int, scale: float, window: Optional[int], partition: int, num_partitions: int,
                      scratch: Optional[torch.Tensor], keep_first: int = 0,
-                     numbering: Optional[torch.Tensor] = None) -> None:
+                     numbering: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None,
+                     gate: Optional[torch.Tensor] = None) -> None:
     """bf16 split-KV attention for a batch of single tokens (row r of qkv belongs to request row r).  `keep_first`:
     with a window, the request's first keys that stay visible; the mma.sync kernel then walks over the kept keys and
-    the window's as one run, and `numbering` (int32 [rows]) is scratch for the merge."""
-    _cuda(qkv, out, k_pages, v_pages, block_table, positions, scratch)
+    the window's as one run, and `numbering` (int32 [rows]) is scratch for the merge.  `sinks`, `gate`: as
+    paged_attention_generic takes them (the kernel that writes a row's final result, the attention kernel or the
+    merge of its partitions, adds the sink's term and applies the gate)."""
+    _cuda(qkv, out, k_pages, v_pages, block_table, positions, scratch, sinks, gate)
     rows = out.shape[0]
+    _check_extras("decode_attention", sinks, gate, out, heads)
+    gate_args = (_ptr(sinks), _ptr(gate), gate.stride(0) if gate is not None else 0)
     _require(qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16
              and v_pages.dtype == torch.bfloat16 and out.is_contiguous() and out.shape[1] == heads * head_dim,
              "decode_attention: bfloat16 tensors are needed")
@@ -1127,18 +1152,18 @@ def decode_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor
         _cuda(numbering)
         _require(numbering is not None and numbering.dtype == torch.int32 and numbering.numel() >= rows,
                  "decode_attention: kept first keys need int32 scratch of one number per row")
-        _check(lib, lib.mir_decode_attention_kept_bf16(
+        _check(lib, lib.mir_decode_attention_extra_bf16(
             qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
             block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), rows, page_size, heads, kv_heads,
             head_dim, scale, int(window), partition, num_partitions, _ptr(scratch),
-            0 if scratch is None else scratch.numel(), _stream(), int(keep_first), numbering.data_ptr()))
+            0 if scratch is None else scratch.numel(), _stream(), int(keep_first), numbering.data_ptr(), *gate_args))
         return
-    _check(lib, lib.mir_decode_attention_paged_bf16(
+    _check(lib, lib.mir_decode_attention_paged_extra_bf16(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0],
         block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), rows, page_size, heads, kv_heads, head_dim,
         scale,
         int(window or 0), partition, num_partitions, _ptr(scratch), 0 if scratch is None else scratch.numel(),
-        _stream()))
+        _stream(), *gate_args))
 
 
 # Whether prompt portions run the tcgen05 attention kernel where it takes the sizes (head_dim 128, pages of 8 to
@@ -1151,13 +1176,18 @@ def prefill_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tenso
                       block_table: torch.Tensor, query_starts: torch.Tensor, context_lens: torch.Tensor,
                       page_size: int, heads: int, kv_heads: int, head_dim: int, scale: float,
                       window: Optional[int], tensor_cores: Optional[bool] = None,
-                      portion_tokens: Optional[int] = None, keep_first: int = 0) -> None:
+                      portion_tokens: Optional[int] = None, keep_first: int = 0,
+                      sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
     """bf16 tensor-core attention for any mix of portions (row r owns tokens query_starts[r]..query_starts[r+1]
     of the packed qkv and out; the rows may be a part of the batch, `portion_tokens` then says how many tokens
     they have together).  `tensor_cores`: True runs the tcgen05 kernel, False the mma.sync kernel, None chooses.
-    `keep_first`: with a window, the first keys of a request that every later query still sees."""
-    _cuda(qkv, out, k_pages, v_pages, block_table, query_starts, context_lens)
+    `keep_first`: with a window, the first keys of a request that every later query still sees.  `sinks`, `gate`: as
+    paged_attention_generic takes them, in the kernels' epilogues (the gate's rows are those of the whole batch, as
+    out's are)."""
+    _cuda(qkv, out, k_pages, v_pages, block_table, query_starts, context_lens, sinks, gate)
     tokens = out.shape[0]
+    _check_extras("prefill_attention", sinks, gate, out, heads)
+    gate_args = (_ptr(sinks), _ptr(gate), gate.stride(0) if gate is not None else 0)
     rows = context_lens.numel()
     _require(qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16
              and v_pages.dtype == torch.bfloat16 and out.is_contiguous() and out.shape[1] == heads * head_dim,
@@ -1171,19 +1201,20 @@ def prefill_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tenso
         portion_tokens = tokens if portion_tokens is None else portion_tokens
         tensor_cores = (PREFILL_TENSOR_CORES and portion_tokens >= PREFILL_TENSOR_CORE_MIN_PORTION * rows
                         and bool(lib.mir_prefill_attention_tc_takes(head_dim, page_size))
-                        and k_pages.is_contiguous() and v_pages.is_contiguous() and scale > 0)
+                        and k_pages.is_contiguous() and v_pages.is_contiguous() and scale > 0
+                        and (gate is None or (gate.data_ptr() % 16 == 0 and gate.stride(0) % 8 == 0)))
     if tensor_cores:
         _require(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.shape == v_pages.shape,
                  "prefill_attention: the tcgen05 kernel reads contiguous [rows, kv_heads, head_dim] pages")
-        _check(lib, lib.mir_prefill_attention_tc_kept_bf16(
+        _check(lib, lib.mir_prefill_attention_tc_extra_bf16(
             qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0],
             block_table.data_ptr(), block_table.shape[1], query_starts.data_ptr(), context_lens.data_ptr(), rows, tokens,
-            page_size, heads, kv_heads, head_dim, scale, int(window or 0), keep_first, _stream()))
+            page_size, heads, kv_heads, head_dim, scale, int(window or 0), keep_first, _stream(), *gate_args))
         return
-    _check(lib, lib.mir_prefill_attention_kept_bf16(
+    _check(lib, lib.mir_prefill_attention_extra_bf16(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], query_starts.data_ptr(), context_lens.data_ptr(), rows, tokens, page_size, heads,
-        kv_heads, head_dim, scale, int(window or 0), keep_first, _stream()))
+        kv_heads, head_dim, scale, int(window or 0), keep_first, _stream(), *gate_args))
 
 
 def set_prefill_softmax_streams(streams: int) -> None:
@@ -1317,26 +1348,14 @@ ACTIVATIONS = ("gelu_tanh", "gelu_erf", "relu2")      # what linear_act applies 
 
 
 def linear_act(x, weight: torch.Tensor, out: torch.Tensor, activation: str, alloc=None) -> None:
-    """out = act(x . weight^T) in the activations' dtype, act one of ACTIVATIONS: the two GELU forms as linear_gelu
-    runs them; "relu2" (the square of relu) as the product and the activation's kernel."""
-    if activation == "relu2":
-        if isinstance(x, NormedResidual):
-            x = x.materialize(alloc)
-        linear(x, weight, out, alloc=alloc)
-        _require(out.is_contiguous(), "linear_act: a contiguous result is needed")
-        relu_squared(out)
-        return
+    """out = act(x . weight^T) in the activations' dtype, act one of ACTIVATIONS: the tanh GELU, the exact GELU
+    0.5 z (1 + erf(z / sqrt 2)) (computed with erff, in the epilogue too) or the square of relu.  bfloat16: one kernel
+    with the activation in its epilogue where our tcgen05 products take the rows (up to few_rows_max on the
+    weight-streaming kernel, where x may be a NormedResidual, a norm folded into this product; from
+    tensor_core_min_rows on the many-rows kernel; the tanh form uses the approximate hardware tanh, whose error is below
+    bfloat16's rounding), else the library product and the activation kernel.  float32: the 32-bit product and that
+    kernel."""
     _require(activation in ACTIVATIONS, f"linear_act: unknown activation {activation!r}")
-    linear_gelu(x, weight, out, alloc=alloc, exact=activation == "gelu_erf")
-
-
-def linear_gelu(x, weight: torch.Tensor, out: torch.Tensor, alloc=None, exact: bool = False) -> None:
-    """out = gelu(x . weight^T) in the activations' dtype: the tanh form, or with `exact` 0.5 z (1 + erf(z / sqrt 2))
-    (computed with erff, in the epilogue too).  bfloat16: one kernel with the activation in its
-    epilogue where our tcgen05 products take the rows (up to few_rows_max on the weight-streaming kernel, where x may
-    be a NormedResidual, a norm folded into this product; from tensor_core_min_rows on the many-rows kernel; the
-    approximate hardware tanh, whose error is below bfloat16's rounding), else the library product and the activation
-    kernel.  float32: the 32-bit product and that kernel."""
     lazy = x if isinstance(x, NormedResidual) else None
     rows = lazy.weighted if lazy is not None else x
     _cuda(rows, weight, out)
@@ -1346,7 +1365,7 @@ def linear_gelu(x, weight: torch.Tensor, out: torch.Tensor, alloc=None, exact: b
             and rows.stride(0) % 8 == 0 and rows.data_ptr() % 16 == 0 and rows.stride(1) == 1 and out.stride(1) == 1
             and weight.is_contiguous() and out.shape == (m, n) and FUSE_GELU_INTO_PRODUCT):
         lib = library("bf16")
-        mode = MODE_GELU_ERF if exact else MODE_GELU
+        mode = {"gelu_tanh": MODE_GELU, "gelu_erf": MODE_GELU_ERF, "relu2": MODE_RELU2}[activation]
         if 0 < m <= min(get_option("few_rows_max"), STREAM_MAX_ROWS) and (lazy is None or m <= NORM_STAT_STRIDE):
             _check(lib, lib.mir_gemm_tc_stream_bf16(
                 mode, rows.data_ptr(), rows.stride(0), weight.data_ptr(), None, out.data_ptr(), out.stride(0), m, n,
@@ -1360,11 +1379,13 @@ def linear_gelu(x, weight: torch.Tensor, out: torch.Tensor, alloc=None, exact: b
     if lazy is not None:
         x = lazy.materialize(alloc)
     linear(x, weight, out, alloc=alloc)
-    _require(out.is_contiguous(), "linear_gelu: a contiguous result is needed")
-    if exact:
-        gelu_erf(out)
-    else:
-        gelu_tanh(out)
+    _require(out.is_contiguous(), "linear_act: a contiguous result is needed")
+    {"gelu_tanh": gelu_tanh, "gelu_erf": gelu_erf, "relu2": relu_squared}[activation](out)
+
+
+def linear_gelu(x, weight: torch.Tensor, out: torch.Tensor, alloc=None, exact: bool = False) -> None:
+    """out = gelu(x . weight^T): linear_act with the tanh form, or with `exact` the erf form."""
+    linear_act(x, weight, out, "gelu_erf" if exact else "gelu_tanh", alloc=alloc)
 
 
 def tensor_core_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
@@ -1445,7 +1466,7 @@ def tensor_core_linear_error() -> int:
 
 
 NORM_STAT_STRIDE = 32        # tokens per row of the sums-of-squares arrays (kNormStatStride of the kernels)
-MODE_STORE, MODE_ACCUM, MODE_F32, MODE_SWIGLU, MODE_GELU, MODE_GELU_ERF = 0, 1, 2, 3, 4, 5
+MODE_STORE, MODE_ACCUM, MODE_F32, MODE_SWIGLU, MODE_GELU, MODE_GELU_ERF, MODE_RELU2 = 0, 1, 2, 3, 4, 5, 6
 
 
 def few_rows_max() -> int:

@@ -173,8 +173,7 @@ class SoftmaxAttention(Mixer):
         s = self.spec
         kept = s.keep_first if s.window is not None else 0
         gate = qkv[:, self.q_width + self.kv_columns:] if s.gate else None      # [tokens, heads * value_dim] view
-        fast = (self.env.dtype == torch.bfloat16 and s.head_dim in kernels.FAST_HEAD_DIMS and s.value_dim == s.head_dim
-                and self.sinks is None and gate is None and s.own_kv)
+        fast = self.env.dtype == torch.bfloat16 and s.head_dim in kernels.FAST_HEAD_DIMS and s.value_dim == s.head_dim
         if fast and kept:
             # kept first keys: single tokens run the mma.sync kernel split over the keys, which walks the kept keys
             # and then the window's (the tcgen05 decode kernel does not know kept keys); portions run as tiles of
@@ -187,12 +186,14 @@ class SoftmaxAttention(Mixer):
                 kernels.decode_attention(qkv[:singles], out[:singles], cache.k_pages, cache.v_pages,
                                          group.block_table[:singles], ctx.positions, cache.page_size, s.heads,
                                          s.kv_heads, s.head_dim, s.scale, s.window, partition, count, scratch,
-                                         keep_first=kept, numbering=ctx.alloc((singles,), torch.int32))
+                                         keep_first=kept, numbering=ctx.alloc((singles,), torch.int32),
+                                         sinks=self.sinks, gate=gate[:singles] if gate is not None else None)
             if singles < ctx.num_rows:
                 kernels.prefill_attention(qkv, out, cache.k_pages, cache.v_pages, group.block_table[singles:],
                                           ctx.query_starts[singles:], ctx.context_lens[singles:], cache.page_size,
                                           s.heads, s.kv_heads, s.head_dim, s.scale, s.window,
-                                          portion_tokens=out.shape[0] - singles, keep_first=kept)
+                                          portion_tokens=out.shape[0] - singles, keep_first=kept, sinks=self.sinks,
+                                          gate=gate)
             return
         if fast:
             # the single-token rows come first in the batch: they run as decoded tokens (keys split over CTAs, the
@@ -205,12 +206,13 @@ class SoftmaxAttention(Mixer):
                 scratch = ctx.alloc((floats,), torch.float32) if floats else None
                 kernels.decode_attention(qkv[:singles], out[:singles], cache.k_pages, cache.v_pages,
                                          group.block_table[:singles], ctx.positions, cache.page_size, s.heads,
-                                         s.kv_heads, s.head_dim, s.scale, s.window, partition, count, scratch)
+                                         s.kv_heads, s.head_dim, s.scale, s.window, partition, count, scratch,
+                                         sinks=self.sinks, gate=gate[:singles] if gate is not None else None)
             if singles < ctx.num_rows:
                 kernels.prefill_attention(qkv, out, cache.k_pages, cache.v_pages, group.block_table[singles:],
                                           ctx.query_starts[singles:], ctx.context_lens[singles:], cache.page_size,
                                           s.heads, s.kv_heads, s.head_dim, s.scale, s.window,
-                                          portion_tokens=out.shape[0] - singles)
+                                          portion_tokens=out.shape[0] - singles, sinks=self.sinks, gate=gate)
             return
         kernels.paged_attention_generic(qkv, out, cache.k_pages, cache.v_pages, group.block_table, ctx.row_of_token,
                                         ctx.positions, cache.page_size, s.heads, s.kv_heads, s.head_dim, s.scale,

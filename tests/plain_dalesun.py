@@ -81,7 +81,8 @@ def frequencies(rot):
 
 
 def _cos_sin(x, positions, rot):
-    angles = positions.to(F64)[:, None] * frequencies(rot)[None, :]           # [n, dims / 2]
+    # the design computes the angle as a 32-bit product of the position and a 32-bit frequency
+    angles = (positions.to(torch.float32)[:, None] * frequencies(rot).to(torch.float32)[None, :]).to(F64)
     shape = [x.shape[0]] + [1] * (x.dim() - 2) + [angles.shape[1]]
     return torch.cos(angles).reshape(shape), torch.sin(angles).reshape(shape)
 
