@@ -1,4 +1,4 @@
-"""`bench.py --design doderax | zufotar`: prefill and decode throughput of a design at layer sizes that resemble a
+"""`bench.py --design doderax | zufotar | dalesun`: prefill and decode throughput of a design at layer sizes that resemble a
 real model's (random weights), beside the dense SwiGLU decoder of equal width, depth and parameter count (and, for
 Zufotar, beside Doderax, the closest model of the framework: recurrent mixers and attention in parallel layers), and
 every kernel the design adds alone, with the fraction of its roofline, beside the like kernel of the closest model.
@@ -220,6 +220,154 @@ def zufotar_kernel_table(s, tools) -> dict:
         calls = [lambda w=w: kernels.linear(hidden_dense, w, out_dense, accumulate=True) for w in w_d]
         table[f"{label}_dense_down_same_work"] = timed(calls, 2.0 * dense_rows * dense_inter * width, flops_peak) if prompt else \
             timed(calls, dense_inter * width * 2, hbm)
+    return table
+
+
+# Dalesun: two retention layers, an attention layer with keys of its own and one that borrows them, in turn.
+DALESUN_SIZES = {
+    "w2048": dict(width=2048, ff=8192, layers=12, heads=16, kv_heads=4, dim=128, window=1024, keep_first=4, vocab=65536,
+                  retention_heads=16, retention_dim=128),
+    "w4096": dict(width=4096, ff=14336, layers=8, heads=32, kv_heads=8, dim=128, window=2048, keep_first=4, vocab=65536,
+                  retention_heads=32, retention_dim=128),
+}
+
+
+def dalesun_config(s: dict) -> dict:
+    heads, dim = s["retention_heads"], s["retention_dim"]
+    retention = {"heads": heads, "dim": dim, "vdim": dim, "rot": {"dims": dim, "base": 1000000.0},
+                 "decay": [1.0 - 2.0 ** (-5.0 - 6.0 * h / max(heads - 1, 1)) for h in range(heads)]}
+    attention = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"],
+                 "scale": s["dim"] ** -0.5, "rot": {"dims": s["dim"] // 2, "base": 20000.0}, "mask": {"size": s["window"]}}
+    mlp = {"kind": "dense", "ff": s["ff"]}
+    layers = []
+    for index in range(s["layers"]):
+        if index % 4 < 2:
+            layers.append({"type": "retention", "mixer": retention, "mlp": mlp})
+        elif index % 4 == 2:
+            layers.append({"type": "attention", "mixer": attention, "mlp": mlp})
+        else:
+            layers.append({"type": "attention", "mixer": dict(attention, kv_from=index - 1), "mlp": mlp})
+    return {"architecture": "Dalesun", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+            "residual_mult": 0.7, "layers": layers}
+
+
+def dalesun_kernel_table(s, tools) -> dict:
+    """Every kernel the design adds or extends, alone, at the sizes of a 2,048-token prompt and of a step of 8 decoded
+    tokens: [microseconds, fraction of its roofline], beside the like kernel of the closest models (Doderax's delta
+    rule with one decay per head; the dense decoder's attention, rotation and feed-forward products)."""
+    import torch
+    from libmir_b200 import kernels
+    timed, copies, rand, device, hbm, flops_peak = (tools[k] for k in ("timed", "copies", "rand", "device", "hbm", "flops_peak"))
+    bf16, f32, i32 = torch.bfloat16, torch.float32, torch.int32
+    width, heads, kv_heads, dim, ff, window = s["width"], s["heads"], s["kv_heads"], s["dim"], s["ff"], s["window"]
+    rh, rd = s["retention_heads"], s["retention_dim"]
+    table = {}
+    alloc = lambda shape, kind: torch.empty(shape, dtype=kind, device=device)
+    note = ["of the bf16 tensor peak; the kernel is 32-bit FMA, one token after the other"]
+    for label, rows, portion in ((f"prefill_{PROMPT}", 1, PROMPT), (f"decode_b{BATCH}", BATCH, 1)):
+        tokens = rows * portion
+        prompt = portion > 1
+        starts = torch.arange(0, tokens + 1, portion, dtype=i32, device=device)
+        slots = torch.arange(rows, dtype=i32, device=device)
+        context = PROMPT if prompt else PROMPT + 1
+        positions = (torch.arange(tokens, dtype=i32, device=device) % portion) + (context - portion)
+        # ---- the retention recurrence (rotation inside), beside the delta rule with one decay per head
+        rwidth = rh * rd
+        packs = copies(lambda: (torch.zeros(rows, rh, rd, rd, device=device, dtype=f32), rand(tokens, 4 * rwidth, scale=0.3)),
+                       rows * rh * rd * rd * 4)
+        inv_freq = torch.rand(rd // 2, device=device, dtype=f32)
+        decays = torch.rand(rh, device=device, dtype=f32) * 0.1 + 0.9
+        read = torch.empty(tokens, rwidth, device=device, dtype=f32)
+        calls = [lambda p=p: kernels.retention_scan(p[1][:, :rwidth], p[1][:, rwidth:2 * rwidth], p[1][:, 2 * rwidth:3 * rwidth],
+                                                    inv_freq, decays, rd ** -0.5, p[0], starts, slots, positions, read,
+                                                    rh, rd, rd) for p in packs]
+        state_bytes = rows * rh * rd * rd * 8 + tokens * rwidth * (3 * 2 + 4)
+        table[f"{label}_retention_scan"] = timed(calls, 4.0 * tokens * rh * rd * rd, flops_peak) + note if prompt else \
+            timed(calls, state_bytes, hbm)
+        packs = copies(lambda: (torch.zeros(rows, rh, rd, rd, device=device, dtype=f32), rand(tokens, 3 * rwidth, dtype=f32, scale=0.1)),
+                       rows * rh * rd * rd * 4)
+        beta = torch.rand(tokens, rh, device=device, dtype=f32)
+        decay = torch.rand(tokens, rh, device=device, dtype=f32) * 0.5 + 0.5
+        calls = [lambda p=p: kernels.delta_rule_scan(p[1], beta, decay, p[0], starts, slots, positions, read, rh, rh, rd, rd)
+                 for p in packs]
+        table[f"{label}_doderax_delta_rule_head"] = timed(calls, 8.0 * tokens * rh * rd * rd, flops_peak) + note if prompt else \
+            timed(calls, rows * rh * rd * rd * 8 + tokens * rwidth * 20, hbm)
+        # ---- unit norm per head with a silu gate; the branch's norm into the residual (Doderax's kernels, one branch)
+        packs = copies(lambda: (rand(tokens, rwidth, dtype=f32), rand(tokens, rwidth)), tokens * rwidth * 6)
+        ones = torch.ones(rd, device=device, dtype=f32)
+        gated = torch.empty(tokens, rwidth, device=device, dtype=bf16)
+        calls = [lambda p=p: kernels.gated_head_norm(p[0], p[1], ones, gated, rh, rd, 1e-6, False) for p in packs]
+        table[f"{label}_gated_head_norm"] = timed(calls, tokens * rwidth * 8, hbm)
+        packs = copies(lambda: (rand(tokens, width, dtype=f32), rand(tokens, width, dtype=f32)), tokens * width * 8)
+        w_a, w_b = rand(width, dtype=f32), rand(width, dtype=f32)
+        calls = [lambda p=p: kernels.add_normed_branches([p[0]], [w_a], p[1], 1e-6, 0.7) for p in packs]
+        table[f"{label}_add_normed_branch"] = timed(calls, tokens * width * 12, hbm)
+        calls = [lambda p=p: kernels.add_normed_branches([p[0], p[0]], [w_a, w_b], p[1], 1e-6, 0.5) for p in packs]
+        table[f"{label}_doderax_add_normed_branches"] = timed(calls, tokens * width * 12, hbm)
+        out_w = torch.empty(tokens, width, device=device, dtype=bf16)
+        calls = [lambda p=p: kernels.rms_norm(p[0], w_a, 1e-6, out_w) for p in packs]
+        table[f"{label}_dense_rms_norm"] = timed(calls, tokens * width * 6, hbm)
+        # ---- q/k norm, rotation of interleaved pairs, keys and values into pages; rows [q | k | v | gate]
+        pages_per_row = -(-(context + PAGE) // PAGE)
+        cache_rows = rows * pages_per_row * PAGE
+        count = max(2, min(24, -(-(300 << 20) // (cache_rows * kv_heads * dim * 4))))
+        k_cache = [rand(cache_rows, kv_heads, dim, scale=0.5) for _ in range(count)]
+        v_cache = [rand(cache_rows, kv_heads, dim, scale=0.5) for _ in range(count)]
+        block_table = torch.arange(rows * pages_per_row, dtype=i32, device=device).view(rows, pages_per_row).contiguous()
+        contexts = torch.full((rows,), context, dtype=i32, device=device)
+        slot_map = (torch.arange(tokens, dtype=i32, device=device) // portion) * (pages_per_row * PAGE) + positions
+        packed_width = (heads + 2 * kv_heads) * dim
+        rows_gated = rand(tokens, packed_width + heads * dim, scale=0.3)
+        rows_plain = rand(tokens, packed_width, scale=0.3)
+        norm_q, norm_k = torch.ones(dim, device=device), torch.ones(dim, device=device)
+        freq = torch.rand(dim // 4, device=device, dtype=f32)
+        moved = tokens * (heads + kv_heads) * dim * 4 + tokens * kv_heads * dim * 4
+        calls = [lambda k=k, v=v: kernels.qk_rope_store(rows_gated, positions, slot_map, freq, norm_q, norm_k, k, v, heads,
+                                                        kv_heads, dim, dim // 2, 1e-6, value_dim=dim, interleaved=True)
+                 for k, v in zip(k_cache, v_cache)]
+        table[f"{label}_qk_rope_store_interleaved"] = timed(calls, moved, hbm)
+        freq_half = torch.rand(dim // 2, device=device, dtype=f32)
+        calls = [lambda k=k, v=v: kernels.qk_rope_store(rows_plain, positions, slot_map, freq_half, norm_q, norm_k, k, v, heads,
+                                                        kv_heads, dim, dim, 1e-6) for k, v in zip(k_cache, v_cache)]
+        table[f"{label}_dense_qk_rope_store"] = timed(calls, moved, hbm)
+        # ---- attention in a window with a sink per head and a sigmoid gate, beside the dense decoder's in the same window
+        qkv = rand(tokens, packed_width + heads * dim, scale=0.3)
+        gate = qkv[:, packed_width:]
+        sinks = rand(heads, dtype=f32)
+        mixed = torch.empty(tokens, heads * dim, device=device, dtype=bf16)
+        scale = dim ** -0.5
+        if prompt:
+            visible = sum(min(p + 1, window) for p in range(PROMPT))
+            flops = 4.0 * visible * dim * heads
+            for extras, name in (({"sinks": sinks, "gate": gate}, "attention_window_sink_gate"), ({}, "dense_attention_window")):
+                calls = [lambda k=k, v=v, e=extras: kernels.prefill_attention(qkv, mixed, k, v, block_table, starts, contexts,
+                                                                               PAGE, heads, kv_heads, dim, scale, window, **e)
+                         for k, v in zip(k_cache, v_cache)]
+                table[f"{label}_{name}"] = timed(calls, flops, flops_peak)
+        else:
+            q_positions = torch.full((tokens,), context - 1, dtype=i32, device=device)
+            partition, parts, floats = kernels.decode_attention_plan(rows, heads, kv_heads, dim, PAGE, context)
+            scratch = torch.empty(max(floats, 1), device=device, dtype=f32)
+            key_bytes = rows * min(window, context) * kv_heads * dim * 2 * 2
+            for extras, name in (({"sinks": sinks, "gate": gate}, "attention_window_sink_gate"), ({}, "dense_attention_window")):
+                calls = [lambda k=k, v=v, e=extras: kernels.decode_attention(qkv, mixed, k, v, block_table, q_positions, PAGE,
+                                                                              heads, kv_heads, dim, scale, window, partition,
+                                                                              parts, scratch if floats else None, **e)
+                         for k, v in zip(k_cache, v_cache)]
+                table[f"{label}_{name}"] = timed(calls, key_bytes, hbm)
+        # ---- the feed-forward's first product with the squared relu in its epilogue, beside the dense decoder's
+        # gate and up product with its silu, at the same multiply-adds
+        x = rand(tokens, width)
+        banks = max(2, min(8, -(-(300 << 20) // (ff * width * 2))))
+        ups = [rand(ff, width, scale=0.03) for _ in range(banks)]
+        hidden = torch.empty(tokens, ff, device=device, dtype=bf16)
+        calls = [lambda w=w: kernels.linear_act(x, w, hidden, "relu2", alloc=alloc) for w in ups]
+        table[f"{label}_up_relu_squared"] = timed(calls, 2.0 * tokens * ff * width, flops_peak) if prompt else \
+            timed(calls, ff * width * 2, hbm)
+        hidden_half = torch.empty(tokens, ff // 2, device=device, dtype=bf16)
+        calls = [lambda w=w: kernels.gate_up_silu(x, w, hidden_half, alloc) for w in ups]
+        table[f"{label}_dense_gate_up_silu_same_work"] = timed(calls, 2.0 * tokens * ff * width, flops_peak) if prompt else \
+            timed(calls, ff * width * 2, hbm)
     return table
 
 
@@ -480,6 +628,21 @@ def run(args, peaks: dict) -> dict:
             entry["zufotar"] = model_numbers(zufotar_config(s), s["vocab"])
             entry["doderax"] = model_numbers(doderax_config(beside), s["vocab"])
             entry["dense_swiglu"] = model_numbers(dense_config(beside), s["vocab"])
+            report[name] = entry
+        return report
+    if args.design == "dalesun":
+        rand = lambda *shape, dtype=bf16, scale=1.0: (torch.randn(*shape, device=device, dtype=f32) * scale).to(dtype)
+        tools = {"timed": timed, "copies": copies, "rand": rand, "device": device, "hbm": hbm, "flops_peak": flops_peak}
+        report = {}
+        for name in [n for n in DALESUN_SIZES if args.design_sizes in ("all", n)]:
+            s = DALESUN_SIZES[name]
+            entry = {"sizes": s}
+            if not args.skip_points:
+                entry["kernels_us_and_fraction_of_roofline"] = dalesun_kernel_table(s, tools)
+                torch.cuda.empty_cache()
+            entry["dalesun"] = model_numbers(dalesun_config(s), s["vocab"])
+            entry["doderax"] = model_numbers(doderax_config(s), s["vocab"])
+            entry["dense_swiglu"] = model_numbers(dense_config(s), s["vocab"])
             report[name] = entry
         return report
     chosen = [name for name in DESIGN_SIZES if args.design_sizes in ("all", name)]
