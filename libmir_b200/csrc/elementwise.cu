@@ -63,8 +63,9 @@ struct NormedBranches {
   const float* weight[4];
   int count;
 };
-__global__ void add_normed_branches_kernel(NormedBranches branches, float* __restrict__ residual, int hidden, float eps,
-                                           float scale) {
+// `rounded` (may be null): the updated residual's rows once more, rounded to bfloat16, for the product that reads them next.
+__global__ void add_normed_branches_kernel(NormedBranches branches, float* __restrict__ residual,
+                                           __nv_bfloat16* __restrict__ rounded, int hidden, float eps, float scale) {
   __shared__ float scratch[32];
   grid_launch_dependents();
   grid_dependency_wait();
@@ -82,14 +83,16 @@ __global__ void add_normed_branches_kernel(NormedBranches branches, float* __res
     float total = 0.0f;
     for (int b = 0; b < branches.count; ++b)
       total += branches.rows[b][(size_t)row * hidden + c] * inverse[b] * branches.weight[b][c];
-    dst[c] += scale * total;
+    const float updated = dst[c] + scale * total;
+    dst[c] = updated;
+    if (rounded) rounded[(size_t)row * hidden + c] = __float2bfloat16(updated);
   }
 }
 
 // The same with 16-byte accesses (hidden a multiple of 4, every pointer 16-byte aligned); the second pass finds the
 // rows in L1.
-__global__ void add_normed_branches_vec4_kernel(NormedBranches branches, float* __restrict__ residual, int hidden,
-                                                float eps, float scale) {
+__global__ void add_normed_branches_vec4_kernel(NormedBranches branches, float* __restrict__ residual,
+                                                __nv_bfloat16* __restrict__ rounded, int hidden, float eps, float scale) {
   __shared__ float scratch[32];
   grid_launch_dependents();
   grid_dependency_wait();
@@ -118,6 +121,12 @@ __global__ void add_normed_branches_vec4_kernel(NormedBranches branches, float* 
     float4 r = dst[c];
     r.x += scale * total.x; r.y += scale * total.y; r.z += scale * total.z; r.w += scale * total.w;
     dst[c] = r;
+    if (rounded) {
+      uint2 packed;
+      *reinterpret_cast<__nv_bfloat162*>(&packed.x) = __floats2bfloat162_rn(r.x, r.y);
+      *reinterpret_cast<__nv_bfloat162*>(&packed.y) = __floats2bfloat162_rn(r.z, r.w);
+      reinterpret_cast<uint2*>(rounded + (size_t)row * hidden)[c] = packed;
+    }
   }
 }
 
@@ -333,24 +342,25 @@ MIR_EXPORT int mir_gelu_tanh(int bf16, void* x, size_t total, cudaStream_t strea
   return mir_check_launch("gelu_tanh");
 }
 
-// rows_b, weight_b: `count` (1 to 4) pointers each, to 32-bit [rows, hidden] and [hidden].
+// rows_b, weight_b: `count` (1 to 4) pointers each, to 32-bit [rows, hidden] and [hidden].  rounded: null, or bfloat16
+// [rows, hidden] that receives the updated residual.
 MIR_EXPORT int mir_add_normed_branches(const float* const* branch_rows, const float* const* branch_weights, int count,
-                                       float* residual, int rows, int hidden, float eps, float scale,
+                                       float* residual, void* rounded, int rows, int hidden, float eps, float scale,
                                        cudaStream_t stream) {
   if (rows == 0) return MIR_OK;
   if (rows < 0 || hidden <= 0 || count < 1 || count > 4) { mir_set_error("add_normed_branches: bad sizes"); return MIR_BAD_ARGUMENT; }
   NormedBranches branches = {};
   branches.count = count;
   for (int b = 0; b < count; ++b) { branches.rows[b] = branch_rows[b]; branches.weight[b] = branch_weights[b]; }
-  bool aligned = (hidden & 3) == 0 && ((uintptr_t)residual & 15) == 0;
+  bool aligned = (hidden & 3) == 0 && ((uintptr_t)residual & 15) == 0 && ((uintptr_t)rounded & 7) == 0;
   for (int b = 0; b < count; ++b)
     aligned = aligned && ((uintptr_t)branch_rows[b] & 15) == 0 && ((uintptr_t)branch_weights[b] & 15) == 0;
   if (aligned)
     return mir_launch("add_normed_branches", add_normed_branches_vec4_kernel, dim3(rows), dim3(hidden >= 4096 ? 256 : 128),
-                      0, stream, 0, branches, residual, hidden, eps, scale);
+                      0, stream, 0, branches, residual, (__nv_bfloat16*)rounded, hidden, eps, scale);
   const int threads = hidden >= 2048 ? 512 : 256;
   return mir_launch("add_normed_branches", add_normed_branches_kernel, dim3(rows), dim3(threads), 0, stream, 0, branches,
-                    residual, hidden, eps, scale);
+                    residual, (__nv_bfloat16*)rounded, hidden, eps, scale);
 }
 
 MIR_EXPORT int mir_rms_norm(int bf16, const float* x, const float* weight, void* out, const int* rows, int n_rows,

@@ -69,33 +69,33 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
   constexpr int TOKENS_PER_WARP = CHUNK / kWarps;
   constexpr int PER_LANE = PADDED / 32;
   constexpr int VALUES_PER_THREAD = (CHUNK * BLOCK_COLUMNS + kWarps * 32 - 1) / (kWarps * 32);
-  float next_q[TOKENS_PER_WARP][PER_LANE], next_k[TOKENS_PER_WARP][PER_LANE];
-  float next_v[VALUES_PER_THREAD];
+  // Lane `lane` of the staging warp owns the channels i = lane + 32 e.  A channel of the first half of the rotated
+  // ones is rotated together with its partner i + half by the lane that owns it (one sine and cosine for the pair, for
+  // q and k alike); the partner's owner has nothing to do there.  `fetch` only issues the loads, in the storage type:
+  // nothing waits for them before `commit`, which runs after the walk over the chunk before.
+  constexpr int PAIRED = (PER_LANE + 1) / 2;                     // 32 e < half <= PADDED / 2 for these e alone
+  T next_q[TOKENS_PER_WARP][PER_LANE], next_k[TOKENS_PER_WARP][PER_LANE];
+  T partner_q[TOKENS_PER_WARP][PAIRED], partner_k[TOKENS_PER_WARP][PAIRED];
+  float next_position[TOKENS_PER_WARP];
+  T next_v[VALUES_PER_THREAD];
   auto fetch = [&](int from) {
     const int count = min(CHUNK, end - from);
 #pragma unroll
     for (int tt = 0; tt < TOKENS_PER_WARP; ++tt) {
       const int t = warp + tt * kWarps;
-      const float position = t < count ? (float)positions[from + t] : 0.0f;
+      const bool live = t < count;
+      next_position[tt] = live ? (float)positions[from + t] : 0.0f;
+      const size_t source = (size_t)(from + (live ? t : 0)) * ld + key_at;
 #pragma unroll
       for (int e = 0; e < PER_LANE; ++e) {
         const int i = lane + 32 * e;
-        next_q[tt][e] = 0.0f; next_k[tt][e] = 0.0f;
-        if (t < count && i < dim) {
-          const size_t source = (size_t)(from + t) * ld + key_at;
-          float qi = to_float(q[source + i]), ki = to_float(k[source + i]);
-          if (i < rotary_dim) {
-            // the first of a pair becomes u cos - v sin, the second v cos + u sin
-            const bool first = i < half;
-            const int partner = first ? i + half : i - half;
-            const float qp = to_float(q[source + partner]), kp = to_float(k[source + partner]);
-            float sine, cosine;
-            sincosf(position * inv_freq[first ? i : partner], &sine, &cosine);
-            qi = first ? qi * cosine - qp * sine : qi * cosine + qp * sine;
-            ki = first ? ki * cosine - kp * sine : ki * cosine + kp * sine;
-          }
-          next_q[tt][e] = qi;
-          next_k[tt][e] = ki * key_scale;
+        const bool mine = live && i < dim && !(i >= half && i < rotary_dim);
+        next_q[tt][e] = mine ? q[source + i] : T(0.0f);
+        next_k[tt][e] = mine ? k[source + i] : T(0.0f);
+        if (e < PAIRED) {
+          const bool paired = live && i < half;
+          partner_q[tt][e] = paired ? q[source + i + half] : T(0.0f);
+          partner_k[tt][e] = paired ? k[source + i + half] : T(0.0f);
         }
       }
     }
@@ -104,7 +104,7 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
       const int index = thread + j * kWarps * 32;
       const int t = index / BLOCK_COLUMNS, c = index - t * BLOCK_COLUMNS;
       next_v[j] = (t < count && first_column + c < value_dim)
-                      ? to_float(v[(size_t)(from + t) * ld + value_at + first_column + c]) : 0.0f;
+                      ? v[(size_t)(from + t) * ld + value_at + first_column + c] : T(0.0f);
     }
   };
   auto commit = [&](int from) {
@@ -118,8 +118,24 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
 #pragma unroll
       for (int e = 0; e < PER_LANE; ++e) {
         const int i = lane + 32 * e;
-        sum = fmaf(next_q[tt][e], next_k[tt][e], sum);
-        at[i] = next_q[tt][e]; at[PADDED + i] = next_k[tt][e];
+        if (32 * e >= half && 32 * e + 32 <= rotary_dim) continue;   // a warp of partners: their owners write them
+        float qi = to_float(next_q[tt][e]), ki = to_float(next_k[tt][e]);
+        if (e < PAIRED && i < half) {
+          // the first of a pair becomes u cos - v sin, the second v cos + u sin
+          const float qp = to_float(partner_q[tt][e]), kp = to_float(partner_k[tt][e]);
+          float sine, cosine;
+          sincosf(next_position[tt] * inv_freq[i], &sine, &cosine);
+          const float q_first = qi * cosine - qp * sine, q_second = qp * cosine + qi * sine;
+          const float k_first = (ki * cosine - kp * sine) * key_scale, k_second = (kp * cosine + ki * sine) * key_scale;
+          sum = fmaf(q_first, k_first, sum);
+          sum = fmaf(q_second, k_second, sum);
+          at[i] = q_first; at[PADDED + i] = k_first;
+          at[i + half] = q_second; at[PADDED + i + half] = k_second;
+        } else if (!(i >= half && i < rotary_dim)) {             // not rotated (or beyond dim: zeros)
+          ki *= key_scale;
+          sum = fmaf(qi, ki, sum);
+          at[i] = qi; at[PADDED + i] = ki;
+        }
       }
       sum = warp_sum(sum);
       if (lane == 0) at[2 * PADDED] = sum;
@@ -128,7 +144,7 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
     for (int j = 0; j < VALUES_PER_THREAD; ++j) {
       const int index = thread + j * kWarps * 32;
       const int t = index / BLOCK_COLUMNS, c = index - t * BLOCK_COLUMNS;
-      if (t < CHUNK) staged[t * ROW + 2 * PADDED + 4 + c] = next_v[j];
+      if (t < CHUNK) staged[t * ROW + 2 * PADDED + 4 + c] = to_float(next_v[j]);
     }
   };
   fetch(start);
@@ -140,7 +156,7 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
     __syncthreads();
     if (from + CHUNK < end) fetch(from + CHUNK);
     const float* in = staged - ROW;
-#pragma unroll 2
+#pragma unroll 4
     for (int t = 0; t < count; ++t) {
       in += ROW;
       const float value = in[2 * PADDED + 4 + local_column];

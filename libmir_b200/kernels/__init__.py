@@ -37,7 +37,8 @@ _SIGNATURES = {
         "mir_embed_pairs": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                             c_longlong, c_longlong, c_float, c_void_p],
         "mir_gelu_tanh": [c_int, c_void_p, c_size_t, c_void_p],
-        "mir_add_normed_branches": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_float, c_void_p],
+        "mir_add_normed_branches": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float,
+                                    c_void_p],
         "mir_short_conv_silu": [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "mir_delta_rule_prepare": [c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
@@ -390,9 +391,14 @@ def gelu_tanh(x: torch.Tensor) -> None:
     _check(lib, lib.mir_gelu_tanh(_is_bf16(x), x.data_ptr(), x.numel(), _stream()))
 
 
-def add_normed_branches(branches, weights, residual: torch.Tensor, eps: float, scale: float) -> None:
-    """residual += scale * sum_b rmsnorm(branches[b]) * weights[b]; every tensor 32-bit, branches [rows, hidden]."""
-    _cuda(residual, *branches, *weights)
+def add_normed_branches(branches, weights, residual: torch.Tensor, eps: float, scale: float,
+                        rounded: Optional[torch.Tensor] = None) -> None:
+    """residual += scale * sum_b rmsnorm(branches[b]) * weights[b]; every tensor 32-bit, branches [rows, hidden].
+    `rounded` (bfloat16 [rows, hidden], contiguous) also receives the updated residual, for the product that reads it
+    next."""
+    _cuda(residual, rounded, *branches, *weights)
+    _require(rounded is None or (rounded.dtype == torch.bfloat16 and rounded.shape == residual.shape
+                                 and rounded.is_contiguous()), "add_normed_branches: rounded is bfloat16 [rows, hidden]")
     rows, hidden = residual.shape
     _require(1 <= len(branches) <= 4 and len(weights) == len(branches) and residual.dtype == torch.float32
              and residual.is_contiguous(), "add_normed_branches: one to four branches and a 32-bit residual")
@@ -403,8 +409,8 @@ def add_normed_branches(branches, weights, residual: torch.Tensor, eps: float, s
     pointers = (c_void_p * len(branches))(*[b.data_ptr() for b in branches])
     weight_pointers = (c_void_p * len(weights))(*[w.data_ptr() for w in weights])
     lib = library("core")
-    _check(lib, lib.mir_add_normed_branches(pointers, weight_pointers, len(branches), residual.data_ptr(), rows, hidden,
-                                            eps, scale, _stream()))
+    _check(lib, lib.mir_add_normed_branches(pointers, weight_pointers, len(branches), residual.data_ptr(), _ptr(rounded),
+                                            rows, hidden, eps, scale, _stream()))
 
 
 def short_conv_silu(x: torch.Tensor, weight: torch.Tensor, tail: torch.Tensor, row_of_token: torch.Tensor,

@@ -175,6 +175,7 @@ class DecoderModel:
         if spec.loop is not None and spec.loop.add_embedding and any((e.opens_pass or 0) > 0 for e in spec.schedule):
             embedded = ctx.alloc(tuple(residual.shape), torch.float32)       # later passes add the embedding's output again
             embedded.copy_(residual)
+        ctx.rounded_residual = None          # (a block leaves one only for the block right behind it, which takes it)
         for run in self._runs(ctx):
             if run.layers is not None:
                 run.execute(ctx, residual)
@@ -189,6 +190,9 @@ class DecoderModel:
             if index + 1 < len(spec.schedule) and (self._native.get(index + 1) is not None
                                                    or spec.schedule[index + 1].opens_pass is not None):
                 ctx.norm_after_block = None          # the next block starts from a residual that this one has not seen
+            ctx.next_reads_residual = (following is not None and getattr(following, "reads_residual_itself", False)
+                                       and self._native.get(index + 1) is None
+                                       and spec.schedule[index + 1].opens_pass is None)
             self.blocks[entry.layer].forward(ctx, ctx.cache_view(index), residual)
         return residual
 

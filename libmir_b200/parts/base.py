@@ -58,12 +58,32 @@ class PartContext:
     Folded norms: before a part runs, its block sets `upcoming_norm` to the norm that will be applied to the
     residual right after the part has added into it (None if unknown); the model sets `norm_after_block` to the norm
     the next block of the schedule starts with.  Whoever changes the residual in another way sets
-    `residual_stats = None`."""
+    `residual_stats = None`.
+
+    Rounded residual: an arrangement whose sublayers read the residual itself needs it in the engine dtype.  The kernel
+    that last updated the residual can write that copy in the same pass; the model sets `next_reads_residual` when the
+    next block of the schedule starts by reading the residual this block leaves, the block then leaves the copy in
+    `rounded_residual`, and the next block takes it (`take_rounded`) instead of casting."""
 
     dtype: Optional[torch.dtype] = None
     upcoming_norm = None
     norm_after_block = None
     residual_stats = None
+    next_reads_residual = False
+    rounded_residual = None
+
+    def take_rounded(self, residual: torch.Tensor) -> torch.Tensor:
+        """The residual in the engine dtype: the copy the block before left, if it left one, else a cast."""
+        rounded, self.rounded_residual = self.rounded_residual, None
+        if rounded is not None and rounded.shape == residual.shape:
+            return rounded
+        return self.cast_residual(residual)
+
+    def rounded_buffer(self, residual: torch.Tensor) -> Optional[torch.Tensor]:
+        """Where a kernel that updates the 32-bit residual may leave its bfloat16 copy; None in the 32-bit engine."""
+        if self.dtype != torch.bfloat16:
+            return None
+        return self.alloc(tuple(residual.shape), torch.bfloat16)
 
     def alloc(self, shape, dtype: torch.dtype) -> torch.Tensor:
         raise NotImplementedError

@@ -186,6 +186,8 @@ class ParallelBlock(Block):
 class OutputNormBlock(Block):
     """x += m * norm_1(mixer(x)), then x += m * norm_2(feed_forward(x)): the norms stand on the branches' results."""
 
+    reads_residual_itself = True         # it starts by reading the residual in the engine dtype
+
     SLOTS = ("mixer_norm", "mixer", "feed_forward_norm", "feed_forward")
 
     def __init__(self, spec, env):
@@ -210,15 +212,21 @@ class OutputNormBlock(Block):
         from .. import kernels
         ctx.upcoming_norm = None             # no norm reads the residual: nothing for a product to prepare
         ctx.residual_stats = None
-        x = ctx.cast_residual(residual)
+        hand_on = ctx.next_reads_residual
+        x = ctx.take_rounded(residual)
         result = ctx.alloc(tuple(residual.shape), torch.float32)
         self.mixer.forward(ctx, cache, x, result, overwrite=True)
-        kernels.add_normed_branches([result], [self.mixer_norm.weight], residual, self.mixer_norm.spec.eps, self.scale)
+        # the kernel that adds the normed branch also writes the new residual in the engine dtype for whoever reads it next
+        rounded = ctx.rounded_buffer(residual) if self.feed_forward is not None or hand_on else None
+        kernels.add_normed_branches([result], [self.mixer_norm.weight], residual, self.mixer_norm.spec.eps, self.scale,
+                                    rounded=rounded)
         if self.feed_forward is not None:
-            x = ctx.cast_residual(residual)
+            x = rounded if rounded is not None else ctx.cast_residual(residual)
             self.feed_forward.forward(ctx, x, result, overwrite=True)
+            rounded = ctx.rounded_buffer(residual) if hand_on else None
             kernels.add_normed_branches([result], [self.feed_forward_norm.weight], residual,
-                                        self.feed_forward_norm.spec.eps, self.scale)
+                                        self.feed_forward_norm.spec.eps, self.scale, rounded=rounded)
+        ctx.rounded_residual = rounded if hand_on else None
         ctx.residual_stats = None
 
 

@@ -92,6 +92,11 @@ def test_branch_norm_into_the_residual(dtype, tol):
         got = on_device(residual)
         kernels.add_normed_branches([on_device(branch)], [on_device(weight)], got, 1e-6, 0.7)
         close(got, want, 2e-6, f"{rows} x {width}")
+        # the same kernel also leaves the new residual rounded to bfloat16 for the next reader: the same bits as a cast
+        again = on_device(residual)
+        rounded = torch.full((rows, width), 7.0, dtype=BF16, device=device())
+        kernels.add_normed_branches([on_device(branch)], [on_device(weight)], again, 1e-6, 0.7, rounded=rounded)
+        assert torch.equal(again, got) and torch.equal(rounded, got.to(BF16)), f"{rows} x {width}: rounded copy"
 
 
 def plain_recurrence(q, k, v, decays, state):
