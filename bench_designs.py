@@ -278,9 +278,11 @@ def dalesun_kernel_table(s, tools) -> dict:
         inv_freq = torch.rand(rd // 2, device=device, dtype=f32)
         decays = torch.rand(rh, device=device, dtype=f32) * 0.1 + 0.9
         read = torch.empty(tokens, rwidth, device=device, dtype=f32)
+        # (a prompt's portion: the rotation's kernel and the walk over what it left, as the mixer runs them)
+        scratch = torch.empty(kernels.retention_prepared_floats(tokens, rh, rd), device=device, dtype=f32) if prompt else None
         calls = [lambda p=p: kernels.retention_scan(p[1][:, :rwidth], p[1][:, rwidth:2 * rwidth], p[1][:, 2 * rwidth:3 * rwidth],
                                                     inv_freq, decays, rd ** -0.5, p[0], starts, slots, positions, read,
-                                                    rh, rd, rd) for p in packs]
+                                                    rh, rd, rd, prepared=scratch) for p in packs]
         state_bytes = rows * rh * rd * rd * 8 + tokens * rwidth * (3 * 2 + 4)
         table[f"{label}_retention_scan"] = timed(calls, 4.0 * tokens * rh * rd * rd, flops_peak) + note if prompt else \
             timed(calls, state_bytes, hbm)

@@ -63,8 +63,8 @@ _SIGNATURES = {
         "mir_wkv_mix": [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                         c_int, c_int, c_int, c_int, c_void_p],
         "mir_retention_scan": [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_float,
-                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                               c_void_p],
+                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                               c_int, c_void_p],
         "mir_wkv_scan": [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "mir_moe_route": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -779,16 +779,28 @@ def wkv_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_raw: torch
 
 
 # --------------------------------------------------------------------------- retention
+def retention_prepared_floats(tokens: int, heads: int, dim: int) -> int:
+    """How many 32-bit numbers retention_scan's `prepared` scratch holds: per token and head the rotated q and k, padded
+    to the kernel's width for heads of `dim` key channels, and q . k."""
+    padded = next((width for width in (32, 64, 128, 192, 256) if dim <= width), dim)
+    return tokens * heads * (2 * padded + 4)
+
+
 def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, inv_freq: Optional[torch.Tensor],
                    decays: torch.Tensor, key_scale: float, state: torch.Tensor, query_starts: torch.Tensor,
                    state_slots: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, heads: int, dim: int,
-                   value_dim: int) -> None:
+                   value_dim: int, prepared: Optional[torch.Tensor] = None) -> None:
     """The retention recurrence over the tokens of each request row, from and into state [slots, heads, value_dim, dim]
     (32-bit): per head S <- decay_h S + k v^T, o = S^T q, with q and k rotated by the token's position (half-split pairs
     of the first 2 * len(inv_freq) channels, 32-bit angles) and k times `key_scale` after the rotation.  q, k [tokens,
     heads * dim] and v [tokens, heads * value_dim]: views with one row stride in the activations' dtype; decays 32-bit
-    [heads]; out 32-bit [tokens, heads * value_dim]."""
-    _cuda(q, k, v, inv_freq, decays, state, query_starts, state_slots, positions, out)
+    [heads]; out 32-bit [tokens, heads * value_dim].  With `prepared` (32-bit scratch of retention_prepared_floats
+    numbers) a step that brings more than single tokens rotates in a kernel of its own, once per token and head, and
+    the walk copies what that left; the results are the same bits either way."""
+    _cuda(q, k, v, inv_freq, decays, state, query_starts, state_slots, positions, out, prepared)
+    _require(prepared is None or (prepared.dtype == torch.float32 and prepared.is_contiguous()
+                                  and prepared.numel() >= retention_prepared_floats(q.shape[0], heads, dim)),
+             "retention_scan: prepared is float32 scratch of retention_prepared_floats numbers")
     tokens = q.shape[0]
     rows = query_starts.numel() - 1
     rotary = 0 if inv_freq is None else 2 * inv_freq.numel()
@@ -806,7 +818,7 @@ def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, inv_freq: 
     _check(lib, lib.mir_retention_scan(_is_bf16(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0),
                                        _ptr(inv_freq), rotary, decays.data_ptr(), float(key_scale), state.data_ptr(),
                                        query_starts.data_ptr(), state_slots.data_ptr(), positions.data_ptr(),
-                                       out.data_ptr(), tokens, rows, heads, dim, value_dim, _stream()))
+                                       out.data_ptr(), _ptr(prepared), tokens, rows, heads, dim, value_dim, _stream()))
 
 
 # --------------------------------------------------------------------------- routed experts

@@ -8,10 +8,11 @@ With h the mixer's input, H heads, key width D and value width V:
     y       = o / rms(o) per head * silu(W_g h)   no weight in the norm
     out     = W_o y
 Per request the mixer keeps S of every head (32-bit) in the request's state slot.  The rotation, the decay, the state
-and the recurrence are 32-bit (csrc/retention.cu rotates while it stages the projections' results, so nothing rotated
-is rounded to the engine's dtype); the projections run in the engine's dtype.  All four projections that read h are
-one product on row-stacked weights [Wq; Wk; Wv; Wg], each segment padded to a multiple of eight rows so that the views
-into the packed result stay 16-byte aligned.
+and the recurrence are 32-bit (csrc/retention.cu rotates while it stages the projections' results, or for prompts'
+portions in a kernel of its own into 32-bit scratch, so nothing rotated is rounded to the engine's dtype); the
+projections run in the engine's dtype.  All four projections that read h are one product on row-stacked weights
+[Wq; Wk; Wv; Wg], each segment padded to a multiple of eight rows so that the views into the packed result stay
+16-byte aligned.
 """
 
 from __future__ import annotations
@@ -88,10 +89,13 @@ class Retention(Mixer):
         kernels.linear(x, self.w_in, packed, alloc=ctx.alloc)
         view = lambda name, width: packed[:, self.offsets[name]:self.offsets[name] + width]
         read = ctx.alloc((tokens, self.v_width), torch.float32)
+        # a step with portions of prompts rotates once per token and head in a kernel of its own
+        prepared = None if ctx.decode_only else ctx.alloc(
+            (kernels.retention_prepared_floats(tokens, s.heads, s.key_dim),), torch.float32)
         kernels.retention_scan(view("q", self.qk_width), view("k", self.qk_width), view("v", self.v_width),
                                self.position.table if self.position is not None else None, self.decays,
                                float(s.key_dim) ** -0.5, state, ctx.query_starts, ctx.state_slots, ctx.positions, read,
-                               s.heads, s.key_dim, s.value_dim)
+                               s.heads, s.key_dim, s.value_dim, prepared=prepared)
         mixed = ctx.alloc((tokens, self.v_width), self.env.dtype)
         kernels.gated_head_norm(read, view("g", self.v_width), self.ones, mixed, s.heads, s.value_dim, s.norm_eps, False)
         if overwrite:

@@ -149,10 +149,18 @@ def test_retention_recurrence_against_the_plain_one(dtype, heads, dim, vdim, rot
             cursor += n
         packed_gpu = on_device(packed)
         out = torch.full((tokens, heads * vdim), 5.0, dtype=torch.float32, device=device())
+        # the same step once more with the rotation in a kernel of its own (scratch full of NaN): the same bits
+        scratch = torch.full((kernels.retention_prepared_floats(tokens, heads, dim),), float("nan"), device=device())
+        other_state, other_out = state.clone(), torch.full_like(out, 6.0)
+        kernels.retention_scan(packed_gpu[:, :heads * dim], packed_gpu[:, heads * dim:2 * heads * dim],
+                               packed_gpu[:, 2 * heads * dim:2 * heads * dim + heads * vdim], inv_freq,
+                               on_device(decays.float()), float(dim) ** -0.5, other_state, query_starts, slot_tensor,
+                               positions, other_out, heads, dim, vdim, prepared=scratch)
         kernels.retention_scan(packed_gpu[:, :heads * dim], packed_gpu[:, heads * dim:2 * heads * dim],
                                packed_gpu[:, 2 * heads * dim:2 * heads * dim + heads * vdim], inv_freq,
                                on_device(decays.float()), float(dim) ** -0.5, state, query_starts, slot_tensor, positions,
                                out, heads, dim, vdim)
+        assert torch.equal(out, other_out) and torch.equal(state, other_state), f"prepared rows, phase {phase}"
         close(out, torch.cat(want), 3e-5, f"read-outs, phase {phase}")
         close(state, want_state, 3e-5, f"states, phase {phase}")
         for untouched in (1, 3, 5):
@@ -169,7 +177,7 @@ def test_a_steps_cut_does_not_change_the_recurrence_at_all():
     inv_freq = on_device(plain.frequencies({"dims": 32, "base": 100.0}).float())
     decays = on_device(torch.tensor([0.9, 0.99, 0.999]))
 
-    def run(cuts):
+    def run(cuts, separate_rotation=False):
         state = torch.zeros(1, heads, vdim, dim, device=device())
         out = torch.zeros(n, heads * vdim, device=device())
         cursor = 0
@@ -178,15 +186,18 @@ def test_a_steps_cut_does_not_change_the_recurrence_at_all():
             cuts = cuts[1:] + cuts[:1]
             rows = packed[cursor:cursor + size]
             _, starts, slots, positions = batch_description([size], [0], [cursor])
+            scratch = torch.empty(kernels.retention_prepared_floats(size, heads, dim), device=device()) \
+                if separate_rotation else None
             kernels.retention_scan(rows[:, :heads * dim], rows[:, heads * dim:2 * heads * dim], rows[:, 2 * heads * dim:],
                                    inv_freq, decays, dim ** -0.5, state, starts, slots, positions, out[cursor:cursor + size],
-                                   heads, dim, vdim)
+                                   heads, dim, vdim, prepared=scratch)
             cursor += size
         return out.cpu(), state.cpu()
     whole = run([n])
     for cuts in ([1], [2, 3, 1, 7, 33], [31, 2]):
-        other = run(cuts)
-        assert torch.equal(whole[0], other[0]) and torch.equal(whole[1], other[1]), cuts
+        for separate_rotation in (False, True):
+            other = run(cuts, separate_rotation)
+            assert torch.equal(whole[0], other[0]) and torch.equal(whole[1], other[1]), (cuts, separate_rotation)
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
