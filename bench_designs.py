@@ -9,6 +9,7 @@ L2 holds); the graph is replayed five times and the median time per launch is ta
 
 from __future__ import annotations
 
+import gc
 import statistics
 
 PROMPT = 2048
@@ -491,6 +492,8 @@ def run(args, peaks: dict) -> dict:
             torch.cuda.synchronize()
             times.append(start.elapsed_time(stop) * 1e3 / launches)
         us = statistics.median(times)
+        del graph                                   # (freed here, not by the collector during some later capture)
+        gc.collect()
         return [round(us, 2), round(work / (us * 1e-6) / peak, 4)]
 
     def copies(make, bytes_each):

@@ -20,6 +20,7 @@ beyond MAX_GRAPHS.
 
 from __future__ import annotations
 
+import gc
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -171,8 +172,16 @@ class DecodeGraph:
         torch.cuda.synchronize()
         before = kernels.launches()
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            self._body()
+        # The cyclic collector stays off while the stream captures: were it to free some older CUDA graph of the
+        # process in the middle, that graph's destruction (not permitted during a capture) would invalidate this one.
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                self._body()
+        finally:
+            if collecting:
+                gc.enable()
         self.launches_per_replay = kernels.launches() - before
         self.graph = graph
         self.step_counter.zero_()
