@@ -158,17 +158,22 @@ __global__ void qk_rope_store_kernel(T* __restrict__ qkv, const int* __restrict_
 // 2 end; tag 100 / 101
 MIR_TRACE_DEFINE(rope)
 
-// bf16, the whole head rotated (rotary_dim == head_dim), half a head a multiple of 8 elements: L = half / 8 lanes
-// take one head, each with two 16-byte pieces (elements 8 l .. 8 l + 7 and their partners half a head further),
-// so a warp works on 32 / L heads at once and every access is 16 bytes wide.
-template <int L>
+// bf16, half a head a multiple of 8 elements: L = half / 8 lanes take one head, each with two 16-byte pieces (elements
+// 8 l .. 8 l + 7 and those half a head further), so a warp works on 32 / L heads at once and every access is 16 bytes
+// wide.  Half-split pairs (the whole head rotated, rotary_dim == head_dim): a lane's two pieces are each other's
+// partners.  INTERLEAVED pairs (2 i, 2 i + 1) of the first rotary_dim channels: both of a pair lie in one piece.
+// row_width: elements from one token's row to the next (what lies behind q, k and v is left alone); queries_only:
+// the rows hold no keys and values.
+template <int L, bool INTERLEAVED>
 __global__ void qk_rope_store_wide_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
                                           const int* __restrict__ slot_mapping, const float* __restrict__ inv_freq,
                                           const float* __restrict__ q_norm, const float* __restrict__ k_norm,
                                           __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
-                                          int heads, int kv_heads, float eps, int write_kv, int units_per_cta) {
+                                          int heads, int kv_heads, float eps, int write_kv, int units_per_cta,
+                                          int rotary_dim, long long row_width, int queries_only) {
   constexpr int HALF = 8 * L, DIM = 2 * HALF, GROUPS = 32 / L;
-  __shared__ float angles[DIM];                      // [HALF] cosines then [HALF] sines of this token
+  const int pairs = rotary_dim / 2;                  // HALF for half-split pairs
+  __shared__ float angles[DIM];                      // [pairs] cosines then [pairs] sines of this token
   grid_launch_dependents();
   MIR_TRACE_BEGIN(rope, (blockIdx.x == 0 && blockIdx.y == 0) || (blockIdx.x == gridDim.x - 1 && blockIdx.y == gridDim.y - 1),
                   100 + (blockIdx.x == 0 && blockIdx.y == 0 ? 0 : 1))
@@ -176,14 +181,14 @@ __global__ void qk_rope_store_wide_kernel(__nv_bfloat16* __restrict__ qkv, const
   const int token = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const int group = lane / L, l = lane % L;
-  const int units = heads + 2 * kv_heads;
-  __nv_bfloat16* row = qkv + (size_t)token * units * DIM;
+  const int units = queries_only ? heads : heads + 2 * kv_heads;
+  __nv_bfloat16* row = qkv + (size_t)token * (size_t)row_width;
   const float position = (float)positions[token];
   const int slot = slot_mapping ? slot_mapping[token] : -1;
   // positions and slots are older than the kernel before this one (the projection): the angles are computed
   // while it may still be running, then this kernel waits for its rows
-  for (int pair = threadIdx.x; pair < HALF; pair += blockDim.x)
-    sincosf(position * inv_freq[pair], &angles[HALF + pair], &angles[pair]);
+  for (int pair = threadIdx.x; pair < pairs; pair += blockDim.x)
+    sincosf(position * inv_freq[pair], &angles[pairs + pair], &angles[pair]);
   grid_dependency_wait();
   __syncthreads();
   if (threadIdx.x == 0) MIR_TRACE_POINT(rope, 1);
@@ -231,12 +236,31 @@ __global__ void qk_rope_store_wide_kernel(__nv_bfloat16* __restrict__ qkv, const
     }
     if (!writes) continue;
     if (!is_value) {
+      if (INTERLEAVED) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float cosine = angles[8 * l + i], sine = angles[HALF + 8 * l + i];
-        const float first = fa[i], second = fb[i];
-        fa[i] = first * cosine - second * sine;
-        fb[i] = first * sine + second * cosine;
+        for (int j = 0; j < 4; ++j) {
+          const int low = 4 * l + j, high = HALF / 2 + 4 * l + j;      // the pairs of this lane's two pieces
+          if (low < pairs) {
+            const float cosine = angles[low], sine = angles[pairs + low];
+            const float first = fa[2 * j], second = fa[2 * j + 1];
+            fa[2 * j] = first * cosine - second * sine;
+            fa[2 * j + 1] = second * cosine + first * sine;
+          }
+          if (high < pairs) {
+            const float cosine = angles[high], sine = angles[pairs + high];
+            const float first = fb[2 * j], second = fb[2 * j + 1];
+            fb[2 * j] = first * cosine - second * sine;
+            fb[2 * j + 1] = second * cosine + first * sine;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float cosine = angles[8 * l + i], sine = angles[HALF + 8 * l + i];
+          const float first = fa[i], second = fb[i];
+          fa[i] = first * cosine - second * sine;
+          fb[i] = first * sine + second * cosine;
+        }
       }
       __nv_bfloat162* ha = reinterpret_cast<__nv_bfloat162*>(&a);
       __nv_bfloat162* hb = reinterpret_cast<__nv_bfloat162*>(&b);
@@ -255,14 +279,21 @@ __global__ void qk_rope_store_wide_kernel(__nv_bfloat16* __restrict__ qkv, const
 template <int L>
 int launch_rope_wide(__nv_bfloat16* qkv, const int* positions, const int* slot_mapping, const float* inv_freq,
                      const float* q_norm, const float* k_norm, __nv_bfloat16* k_pages, __nv_bfloat16* v_pages, int tokens,
-                     int heads, int kv_heads, float eps, int write_kv, cudaStream_t stream) {
-  const int units = heads + 2 * kv_heads;
+                     int heads, int kv_heads, float eps, int write_kv, cudaStream_t stream, int interleaved = 0,
+                     int rotary_dim = 16 * L, long long row_width = 0, int queries_only = 0) {
+  const int units = queries_only ? heads : heads + 2 * kv_heads;
+  if (row_width == 0) row_width = (long long)units * 16 * L;
   const bool many = tokens >= 256;                     // one CTA of 8 warps per token, else CTAs of 4 warps
   const int threads = many ? 256 : 128;
   const int units_per_cta = many ? units : 4 * (32 / L);
   const dim3 grid(tokens, (units + units_per_cta - 1) / units_per_cta);
-  return mir_launch_with(mir_pdl_for_streaming(), "qk_rope_store", qk_rope_store_wide_kernel<L>, grid, dim3(threads), 0, stream, 0, qkv, positions,
-                    slot_mapping, inv_freq, q_norm, k_norm, k_pages, v_pages, heads, kv_heads, eps, write_kv, units_per_cta);
+  if (interleaved)
+    return mir_launch_with(mir_pdl_for_streaming(), "qk_rope_store", qk_rope_store_wide_kernel<L, true>, grid, dim3(threads),
+                           0, stream, 0, qkv, positions, slot_mapping, inv_freq, q_norm, k_norm, k_pages, v_pages, heads,
+                           kv_heads, eps, write_kv, units_per_cta, rotary_dim, row_width, queries_only);
+  return mir_launch_with(mir_pdl_for_streaming(), "qk_rope_store", qk_rope_store_wide_kernel<L, false>, grid, dim3(threads),
+                         0, stream, 0, qkv, positions, slot_mapping, inv_freq, q_norm, k_norm, k_pages, v_pages, heads,
+                         kv_heads, eps, write_kv, units_per_cta, rotary_dim, row_width, queries_only);
 }
 
 template <typename T>
@@ -312,17 +343,18 @@ MIR_EXPORT int mir_qk_rope_store(int bf16, void* qkv, const int* positions, cons
     return MIR_BAD_ARGUMENT;
   }
   if (row_stride == packed_width && !queries_only) row_stride = 0;
-  if (bf16 && !interleaved && row_stride == 0 && rotary_dim == head_dim && value_dim == head_dim && head_dim % 16 == 0 &&
+  const bool wide_rotation = interleaved ? true : (rotary_dim == head_dim && row_stride == 0);
+  if (bf16 && wide_rotation && row_stride % 8 == 0 && value_dim == head_dim && head_dim % 16 == 0 &&
       ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0) {
     __nv_bfloat16* q = (__nv_bfloat16*)qkv;
     __nv_bfloat16* kp = (__nv_bfloat16*)k_pages;
     __nv_bfloat16* vp = (__nv_bfloat16*)v_pages;
     switch (head_dim / 16) {                             // lanes per head
-      case 1: return launch_rope_wide<1>(q, positions, slot_mapping, inv_freq, q_norm, k_norm, kp, vp, tokens, heads, kv_heads, eps, write_kv, stream);
-      case 2: return launch_rope_wide<2>(q, positions, slot_mapping, inv_freq, q_norm, k_norm, kp, vp, tokens, heads, kv_heads, eps, write_kv, stream);
-      case 4: return launch_rope_wide<4>(q, positions, slot_mapping, inv_freq, q_norm, k_norm, kp, vp, tokens, heads, kv_heads, eps, write_kv, stream);
-      case 8: return launch_rope_wide<8>(q, positions, slot_mapping, inv_freq, q_norm, k_norm, kp, vp, tokens, heads, kv_heads, eps, write_kv, stream);
-      case 16: return launch_rope_wide<16>(q, positions, slot_mapping, inv_freq, q_norm, k_norm, kp, vp, tokens, heads, kv_heads, eps, write_kv, stream);
+      case 1: return launch_rope_wide<1>(q, positions, slot_mapping, inv_freq, q_norm, k_norm, kp, vp, tokens, heads, kv_heads, eps, write_kv, stream, interleaved, rotary_dim, row_stride, queries_only);
+      case 2: return launch_rope_wide<2>(q, positions, slot_mapping, inv_freq, q_norm, k_norm, kp, vp, tokens, heads, kv_heads, eps, write_kv, stream, interleaved, rotary_dim, row_stride, queries_only);
+      case 4: return launch_rope_wide<4>(q, positions, slot_mapping, inv_freq, q_norm, k_norm, kp, vp, tokens, heads, kv_heads, eps, write_kv, stream, interleaved, rotary_dim, row_stride, queries_only);
+      case 8: return launch_rope_wide<8>(q, positions, slot_mapping, inv_freq, q_norm, k_norm, kp, vp, tokens, heads, kv_heads, eps, write_kv, stream, interleaved, rotary_dim, row_stride, queries_only);
+      case 16: return launch_rope_wide<16>(q, positions, slot_mapping, inv_freq, q_norm, k_norm, kp, vp, tokens, heads, kv_heads, eps, write_kv, stream, interleaved, rotary_dim, row_stride, queries_only);
       default: break;                                    // other head sizes: the kernel below
     }
   }
