@@ -235,10 +235,10 @@ DALESUN_SIZES = {
 
 def dalesun_config(s: dict) -> dict:
     heads, dim = s["retention_heads"], s["retention_dim"]
-    retention = {"heads": heads, "dim": dim, "vdim": dim, "rot": {"dims": dim, "base": 1000000.0},
-                 "decay": [1.0 - 2.0 ** (-5.0 - 6.0 * h / max(heads - 1, 1)) for h in range(heads)]}
+    retention = {"heads": heads, "dim": dim, "vdim": dim, "rot": {"dims": dim, "base": 500000.0},
+                 "decay": [1.0 - 2.0 ** (-4.0 - 8.0 * h / heads) for h in range(heads)]}
     attention = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"],
-                 "scale": s["dim"] ** -0.5, "rot": {"dims": s["dim"] // 2, "base": 20000.0}, "mask": {"size": s["window"]}}
+                 "scale": s["dim"] ** -0.5, "rot": {"dims": s["dim"] // 2, "base": 10000.0}, "mask": {"size": s["window"]}}
     mlp = {"kind": "dense", "ff": s["ff"]}
     layers = []
     for index in range(s["layers"]):
@@ -248,8 +248,8 @@ def dalesun_config(s: dict) -> dict:
             layers.append({"type": "attention", "mixer": attention, "mlp": mlp})
         else:
             layers.append({"type": "attention", "mixer": dict(attention, kv_from=index - 1), "mlp": mlp})
-    return {"architecture": "Dalesun", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
-            "residual_mult": 0.7, "layers": layers}
+    return {"architecture": "Dalesun", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5},
+            "residual_mult": 0.5, "layers": layers}
 
 
 def dalesun_kernel_table(s, tools) -> dict:
@@ -303,7 +303,7 @@ def dalesun_kernel_table(s, tools) -> dict:
         table[f"{label}_gated_head_norm"] = timed(calls, tokens * rwidth * 8, hbm)
         packs = copies(lambda: (rand(tokens, width, dtype=f32), rand(tokens, width, dtype=f32)), tokens * width * 8)
         w_a, w_b = rand(width, dtype=f32), rand(width, dtype=f32)
-        calls = [lambda p=p: kernels.add_normed_branches([p[0]], [w_a], p[1], 1e-6, 0.7) for p in packs]
+        calls = [lambda p=p: kernels.add_normed_branches([p[0]], [w_a], p[1], 1e-6, 0.6) for p in packs]
         table[f"{label}_add_normed_branch"] = timed(calls, tokens * width * 12, hbm)
         calls = [lambda p=p: kernels.add_normed_branches([p[0], p[0]], [w_a, w_b], p[1], 1e-6, 0.5) for p in packs]
         table[f"{label}_doderax_add_normed_branches"] = timed(calls, tokens * width * 12, hbm)

@@ -69,7 +69,7 @@ DALESUN_C = {   # heads of 64 channels (tensor cores in bfloat16), widths that a
 DALESUN_D = {   # heads of 128 channels; a borrower with a narrower window behind a lender without one
     "architecture": "Dalesun", "vocab": 97, "width": 128, "norm": {"eps": 1e-6}, "residual_mult": 0.25,
     "layers": [
-        _layer(_retention(128, 64, (0.99, 0.9), rot=(128, 1000000.0)), 200),
+        _layer(_retention(128, 64, (0.99, 0.9), rot=(128, 500000.0)), 200),
         _layer(_attention(4, 2, 128, 128, 0.09, rot=(32, 10000.0)), None),
         _layer(_attention(4, 2, 128, 128, 0.07, window=70, rot=(32, 10000.0), kv_from=1), 48),
     ],
@@ -122,7 +122,7 @@ def random_config(rng) -> dict:
         if rng.random() < 0.2:
             return None
         dims = int(rng.choice([d for d in (2, 4, 6, 8, 16, 32, 64, 128) if d <= dim]))
-        return (dims, float(rng.choice([50.0, 10000.0, 1000000.0])))
+        return (dims, float(rng.choice([50.0, 10000.0, 500000.0])))
 
     def attention(lenders):
         if lenders and rng.random() < 0.4:

@@ -88,14 +88,14 @@ def test_branch_norm_into_the_residual(dtype, tol):
     torch.manual_seed(3)
     for rows, width in ((1, 8), (5, 100), (130, 192), (3, 2050)):
         residual, branch, weight = torch.randn(rows, width), torch.randn(rows, width) * 30.0, 1.0 + torch.randn(width) * 0.3
-        want = residual.double() + 0.7 * plain.unit_rms(branch.double(), 1e-6) * weight.double()
+        want = residual.double() + 0.6 * plain.unit_rms(branch.double(), 1e-6) * weight.double()
         got = on_device(residual)
-        kernels.add_normed_branches([on_device(branch)], [on_device(weight)], got, 1e-6, 0.7)
+        kernels.add_normed_branches([on_device(branch)], [on_device(weight)], got, 1e-6, 0.6)
         close(got, want, 2e-6, f"{rows} x {width}")
         # the same kernel also leaves the new residual rounded to bfloat16 for the next reader: the same bits as a cast
         again = on_device(residual)
         rounded = torch.full((rows, width), 7.0, dtype=BF16, device=device())
-        kernels.add_normed_branches([on_device(branch)], [on_device(weight)], again, 1e-6, 0.7, rounded=rounded)
+        kernels.add_normed_branches([on_device(branch)], [on_device(weight)], again, 1e-6, 0.6, rounded=rounded)
         assert torch.equal(again, got) and torch.equal(rounded, got.to(BF16)), f"{rows} x {width}: rounded copy"
 
 
@@ -218,7 +218,7 @@ def test_head_unit_norm_with_a_silu_gate(dtype, tol):
 @pytest.mark.parametrize("dtype,tol", DTYPES)
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim,rotary,borrower", [(6, 2, 32, 16, 16, False), (1, 1, 16, 16, 16, False),
                                                                      (4, 1, 64, 64, 24, True), (3, 3, 20, 12, 0, False),
-                                                                     (4, 2, 128, 128, 32, True), (8, 1, 96, 40, 48, False)])
+                                                                     (4, 2, 128, 128, 32, True), (6, 1, 80, 40, 40, False)])
 def test_queries_and_keys_are_normed_rotated_in_interleaved_pairs_and_stored(dtype, tol, heads, kv_heads, dim, vdim,
                                                                             rotary, borrower):
     """Packed rows [q | k | v | gate] (a borrower: [q | gate]): per-head RMS norm with one plain weight for all heads,
@@ -307,7 +307,7 @@ def scatter_into_pool(ks, vs, page, rng, dtype):
 # which kernel a case runs: the reference kernel, the mma.sync kernels, the tcgen05 kernels
 ATTENTION_CASES = [
     # dtype, heads, kv_heads, dim, vdim, page, window, path
-    (torch.float32, 6, 2, 32, 16, 8, 24, "reference"), (BF16, 8, 1, 96, 96, 16, 40, "reference"),
+    (torch.float32, 6, 2, 32, 16, 8, 24, "reference"), (BF16, 6, 1, 80, 80, 16, 40, "reference"),
     (torch.float32, 1, 1, 16, 16, 4, 1, "reference"), (BF16, 3, 3, 20, 12, 4, None, "reference"),
     (BF16, 4, 1, 64, 64, 8, 50, "mma"), (BF16, 6, 3, 64, 64, 16, None, "mma"), (BF16, 4, 2, 128, 128, 16, 70, "mma"),
     (BF16, 4, 2, 128, 128, 16, 70, "tcgen05"), (BF16, 8, 1, 128, 128, 32, None, "tcgen05"),
