@@ -263,10 +263,11 @@ retention_scan_prepared_kernel(const float* __restrict__ prepared, const T* __re
   constexpr int PADDED = kLanes * PER;
   constexpr int PREPARED = 2 * PADDED + 4;                        // q | k | q . k
   constexpr int ROW = PREPARED + BLOCK_COLUMNS;                   // and v of this CTA's columns
-  constexpr int CHUNK = PADDED <= 64 ? 32 : (PADDED <= 128 ? 16 : 8);
+  constexpr int CHUNK = PADDED <= 128 ? 16 : 8;
   constexpr int PIECES = PREPARED / 4;                            // 16-byte pieces of a prepared row
   constexpr int VALUES_PER_THREAD = (CHUNK * BLOCK_COLUMNS + kWarps * 32 - 1) / (kWarps * 32);
   __shared__ __align__(16) float staged[2][CHUNK * ROW];
+  __shared__ __align__(16) float partial[CHUNK][kWarps * 32];     // per token: every lane's part of its column's read-out
   grid_launch_dependents();
   grid_dependency_wait();
   const int lane = threadIdx.x, warp = threadIdx.y;
@@ -347,11 +348,27 @@ retention_scan_prepared_kernel(const float* __restrict__ prepared, const T* __re
         s[m + 2] = fmaf(s[m + 2], decay, key.z * value);
         s[m + 3] = fmaf(s[m + 3], decay, key.w * value);
       }
-      float total = (read[0] + read[1]) + (read[2] + read[3]);
+      partial[t][thread] = (read[0] + read[1]) + (read[2] + read[3]);
+    }
+    __syncthreads();
+    // the lanes' parts of a column are summed as the butterfly of shuffles in the kernel above sums them (neighbours
+    // first, then pairs of pairs, ...), so that the bits are the same; one (token, column) a thread and pass
+    for (int index = thread; index < count * BLOCK_COLUMNS; index += kWarps * 32) {
+      const int t = index / BLOCK_COLUMNS, c = index - t * BLOCK_COLUMNS;
+      float parts[kLanes];
 #pragma unroll
-      for (int step = 1; step < kLanes; step <<= 1) total += __shfl_xor_sync(0xffffffffu, total, step);
-      if (l == 0 && active)
-        out[(size_t)(from + t) * out_width + value_at + column] = fmaf(in[2 * PADDED], value, decay * total);
+      for (int i = 0; i < kLanes; i += 4) {
+        const float4 four = *reinterpret_cast<const float4*>(&partial[t][c * kLanes + i]);
+        parts[i] = four.x; parts[i + 1] = four.y; parts[i + 2] = four.z; parts[i + 3] = four.w;
+      }
+#pragma unroll
+      for (int width = 1; width < kLanes; width <<= 1)
+#pragma unroll
+        for (int i = 0; i < kLanes; i += 2 * width) parts[i] += parts[i + width];
+      const float* in = staged[stage] + t * ROW;
+      if (first_column + c < value_dim)
+        out[(size_t)(from + t) * out_width + value_at + first_column + c] =
+            fmaf(in[2 * PADDED], in[PREPARED + c], decay * parts[0]);
     }
   }
   if (!active) return;
