@@ -148,6 +148,38 @@ class RmsNormSpec(PartSpec):
 
 
 @dataclass(frozen=True)
+class LayerNormSpec(PartSpec):
+    """y = (x - mean) / sqrt(variance + eps) * w + b, the variance being the mean of the squared deviations.  `tensor`
+    and `bias_tensor` are the local names of weight and bias ("" where the checkpoint names the norm itself)."""
+
+    size: int = 0
+    eps: float = 1e-5
+    tensor: str = "weight"
+    bias_tensor: str = "bias"
+    kind: str = field(init=False, default="layer_norm")
+
+
+@dataclass(frozen=True)
+class StreamMixSpec(PartSpec):
+    """How one sublayer reads and writes a residual kept as `streams` copies (hyper-connections): three stored 32-bit
+    tensors, `in` [S] (the sublayer's input is sum_s in[s] x_s), `mix` [S, S] indexed [from, to] and `out` [S]
+    (x_t <- sum_s mix[s, t] x_s + out[t] * the sublayer's result, all streams at once from the old ones)."""
+
+    streams: int = 0
+    kind: str = field(init=False, default="stream_mix")
+
+
+@dataclass(frozen=True)
+class DistanceBiasSpec:
+    """A learned bias on attention scores by the distance n = query position - key position: the stored table has
+    `rows` buckets (one column per query head); bucket(n) = n below rows // 2, and from there on
+    min(rows - 1, rows // 2 + floor(ln(n / (rows // 2)) / ln(farthest / (rows // 2)) * (rows - rows // 2)))."""
+
+    rows: int
+    farthest: float
+
+
+@dataclass(frozen=True)
 class YarnScaling:
     """Frequencies stretched by `factor` where a pair turns fewer than `slow` times over `original` positions, kept
     where it turns more than `fast` times, blended linearly (by pair index) in between; cos and sin are multiplied by
@@ -196,6 +228,21 @@ class SoftmaxAttentionSpec(PartSpec):
     sinks: bool = False
     gate: bool = False
     own_kv: bool = True
+    # fixed_sink: every head's sink is this constant of the design instead of a stored number (0: one is added to the
+    # softmax's denominator).  gate_per_head: the gate's projection has one row per query head, whose sigmoid
+    # multiplies the whole head.  qk_norm_span: "head" norms every head by itself with one weight [head_dim] for all
+    # heads; "projection" norms q as a whole and k as a whole over all their heads, with weights of that width.
+    # qk_norm_weight False: the norm has no weights.  qk_norm_after_rotation: the per-head norm follows the rotation.
+    # softcap: score <- softcap * tanh(score / softcap) after the scale.  distance_bias: a stored table (tensor
+    # `rel_bias` [rows, heads]) added to the scores after the cap, by the bucket of the distance; `scale` does not
+    # multiply it.
+    fixed_sink: Optional[float] = None
+    gate_per_head: bool = False
+    qk_norm_span: str = "head"
+    qk_norm_weight: bool = True
+    qk_norm_after_rotation: bool = False
+    softcap: Optional[float] = None
+    distance_bias: Optional[DistanceBiasSpec] = None
     kind: str = field(init=False, default="softmax_attention")
 
     @property
@@ -259,11 +306,14 @@ class WkvSpec(PartSpec):
 @dataclass(frozen=True)
 class RoutedExpertsSpec(PartSpec):
     """A mixture of gated experts (down(silu(gate x) * up x)), `top` of `experts` per token (parts/experts.py).
-    Router: 32-bit logits, `score` "sigmoid"; with `correction` a stored bias is added to the scores for the choice
-    only; experts lie in `groups` equal groups of neighbours of which the `keep_groups` best (by the sum of a group's
-    two largest choice scores) may be chosen from; the chosen scores are divided by their sum and multiplied by
-    `scale`.  `shared_size` > 0: an expert of that width runs for every token, times the sigmoid of one number per
-    token if `shared_gate`."""
+    Router: 32-bit logits, `score` "sigmoid" or "softmax" (over all the router's outputs); with `correction` a stored
+    bias is added to the scores for the choice only; experts lie in `groups` equal groups of neighbours of which the
+    `keep_groups` best (`group_score` "top2": by the sum of a group's two largest choice scores, "max": by its largest)
+    may be chosen from; the chosen scores are divided by their sum and multiplied by `scale`.  `identity` > 0: the
+    router has that many more outputs behind the experts', identity experts without tensors whose result is the
+    feed-forward's input itself; they take part in scores, groups and choice like the others (`experts` counts only
+    the experts with weights).  `shared_size` > 0: an expert of that width runs for every token, times the sigmoid of
+    one number per token if `shared_gate`."""
 
     hidden_size: int = 0
     expert_size: int = 0
@@ -275,6 +325,9 @@ class RoutedExpertsSpec(PartSpec):
     correction: bool = True
     shared_size: int = 0
     shared_gate: bool = True
+    score: str = "sigmoid"
+    group_score: str = "top2"
+    identity: int = 0
     kind: str = field(init=False, default="routed_experts")
 
 
@@ -348,8 +401,10 @@ class LayerSpec:
     arrangement to the sub-prefix of its tensors, so names are data of the architecture.
     Arrangements: "pre_norm" (a norm before each of the two branches, one after the other), "parallel" (both
     branches read the same residual and their results are added to it together: through one norm, `mixer_norm`, if
-    `feed_forward_norm` is None, else each through a norm of its own) and "output_norm" (each branch reads the
-    residual itself and its RESULT goes through the norm: x += residual_scale * norm(branch(x)), one after the other).
+    `feed_forward_norm` is None, else each through a norm of its own), "output_norm" (each branch reads the
+    residual itself and its RESULT goes through the norm: x += residual_scale * norm(branch(x)), one after the other)
+    and "streams" (the residual is ModelSpec.streams copies; each branch reads a mix of them through its norm and
+    writes into all of them as `mixer_streams` / `feed_forward_streams`, StreamMixSpec, say).
     """
 
     prefix: str
@@ -360,6 +415,8 @@ class LayerSpec:
     names: Mapping[str, str]
     arrangement: str = "pre_norm"
     residual_scale: float = 1.0           # what a branch's (normed) result is multiplied by ("output_norm" only)
+    mixer_streams: Optional[PartSpec] = None          # ("streams" only) how the mixer reads and writes the streams
+    feed_forward_streams: Optional[PartSpec] = None   # the same for the feed-forward
 
 
 @dataclass(frozen=True)
@@ -424,10 +481,17 @@ class ModelSpec:
     head: HeadSpec
     strip_prefixes: tuple = ()      # checkpoint prefixes that may wrap every name
     loop: Optional[LoopSpec] = None
+    # streams > 0: the residual is that many copies per token, all equal to the embedding's output at the start and
+    # summed before the final norm; every layer then has the "streams" arrangement
+    streams: int = 0
 
     def validate(self) -> None:
         if not self.layers:
             raise ConfigError("a model needs at least one layer")
+        for index, layer in enumerate(self.layers):
+            if (layer.arrangement == "streams") != (self.streams > 0):
+                raise ConfigError(f"layer {index}: the \"streams\" arrangement and a residual of several streams "
+                                  "(ModelSpec.streams) go together")
         for index, entry in enumerate(self.schedule):
             if not 0 <= entry.layer < len(self.layers):
                 raise ConfigError(f"schedule entry {index} names layer {entry.layer}, the model has {len(self.layers)}")

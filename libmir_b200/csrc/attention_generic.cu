@@ -18,7 +18,11 @@
 // value_dim elements of the keys themselves (a latent that is read both ways; v_pages is then k_pages).
 // sinks (one 32-bit number per query head, or none): exp(sink - max) is added to the softmax's denominator once; it
 // has no key and no value and is not scaled.  gate (rows of the activations' type with a stride of their own, or
-// none): the head's result is multiplied by the sigmoid of its gate elements before it is stored.
+// none): the head's result is multiplied by the sigmoid of its gate elements before it is stored; gate_per_head: a
+// gate row holds one number per head instead of one per element.
+// softcap > 0: score <- softcap * tanh(score / softcap) after the scale.  rel_bias ([rel_rows, heads] 32-bit, or none):
+// the row min(position - key, rel_rows - 1) of head h is added to the score after the cap (a bias by distance whose
+// buckets the host has spread out into one row per distance; from the last row on it no longer changes).
 #include <cfloat>
 #include "common.cuh"
 
@@ -33,7 +37,8 @@ __global__ void paged_attention_generic_kernel(
     const T* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
     const int* __restrict__ row_of_token, const int* __restrict__ positions, int page_size, int heads, int kv_heads,
     int head_dim, int value_dim, int value_row_width, float scale, int window, int keep_first,
-    const float* __restrict__ sinks, const T* __restrict__ gate, size_t gate_stride) {
+    const float* __restrict__ sinks, const T* __restrict__ gate, size_t gate_stride, int gate_per_head, float softcap,
+    const float* __restrict__ rel_bias, int rel_rows) {
   __shared__ float q_shared[kWarpsPerBlock][kMaxHeadDim];
   const int lane = threadIdx.x;
   const int warp = threadIdx.y;
@@ -84,6 +89,8 @@ __global__ void paged_attention_generic_kernel(
         for (int d = 0; d < head_dim; ++d) dot = fmaf(q_shared[warp][d], to_float(k_row[d]), dot);
       }
       score = dot * scale;
+      if (softcap > 0.0f) score = softcap * tanhf(score / softcap);
+      if (rel_bias != nullptr) score += rel_bias[(size_t)min(position - key, rel_rows - 1) * heads + head];
     }
     const float next_max = fmaxf(running_max, warp_max(score));
     const float correction = expf(running_max - next_max);
@@ -114,14 +121,15 @@ __global__ void paged_attention_generic_kernel(
     for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] *= correction;
   }
   T* out_row = out + ((size_t)token * heads + head) * value_dim;
-  const T* gate_row = gate != nullptr ? gate + (size_t)token * gate_stride + (size_t)head * value_dim : nullptr;
+  const T* gate_row = gate != nullptr ? gate + (size_t)token * gate_stride + (size_t)head * (gate_per_head ? 1 : value_dim)
+                                      : nullptr;
   const float inverse = denominator > 0.0f ? 1.0f / denominator : 0.0f;   // a padded row has no keys
 #pragma unroll
   for (int i = 0; i < kMaxHeadDim / 32; ++i) {
     const int d = lane + 32 * i;
     if (d < value_dim) {
       float result = acc[i] * inverse;
-      if (gate_row != nullptr) result *= 1.0f / (1.0f + expf(-to_float(gate_row[d])));
+      if (gate_row != nullptr) result *= 1.0f / (1.0f + expf(-to_float(gate_row[gate_per_head ? 0 : d])));
       out_row[d] = from_float<T>(result);
     }
   }
@@ -134,6 +142,7 @@ MIR_EXPORT int mir_paged_attention_generic(int bf16, const void* q, long long q_
                                            int page_size, int heads, int kv_heads, int head_dim, int value_dim,
                                            float scale, int window, int keep_first, int value_row_width,
                                            const float* sinks, const void* gate, long long gate_stride,
+                                           int gate_per_head, float softcap, const float* rel_bias, int rel_rows,
                                            cudaStream_t stream) {
   if (tokens == 0) return MIR_OK;
   if (tokens < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || page_size <= 0 || table_width <= 0 ||
@@ -151,6 +160,7 @@ MIR_EXPORT int mir_paged_attention_generic(int bf16, const void* q, long long q_
     return MIR_BAD_ARGUMENT;
   }
   if (value_row_width <= 0) value_row_width = value_dim;
+  if (rel_bias != nullptr && rel_rows <= 0) { mir_set_error("paged_attention: a bias by distance needs rows"); return MIR_BAD_ARGUMENT; }
   const dim3 grid(tokens, (heads + kWarpsPerBlock - 1) / kWarpsPerBlock);
   const dim3 block(32, kWarpsPerBlock);
   if (bf16)
@@ -158,11 +168,12 @@ MIR_EXPORT int mir_paged_attention_generic(int bf16, const void* q, long long q_
         (const __nv_bfloat16*)q, (size_t)q_token_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pages,
         (const __nv_bfloat16*)v_pages, block_table, table_width, row_of_token, positions, page_size, heads, kv_heads,
         head_dim, value_dim, value_row_width, scale, window, keep_first, sinks, (const __nv_bfloat16*)gate,
-        (size_t)gate_stride);
+        (size_t)gate_stride, gate_per_head, softcap, rel_bias, rel_rows);
   else
     paged_attention_generic_kernel<<<grid, block, 0, stream>>>(
         (const float*)q, (size_t)q_token_stride, (float*)out, (const float*)k_pages, (const float*)v_pages,
         block_table, table_width, row_of_token, positions, page_size, heads, kv_heads, head_dim, value_dim,
-        value_row_width, scale, window, keep_first, sinks, (const float*)gate, (size_t)gate_stride);
+        value_row_width, scale, window, keep_first, sinks, (const float*)gate, (size_t)gate_stride, gate_per_head, softcap,
+        rel_bias, rel_rows);
   return mir_check_launch("paged_attention_generic");
 }

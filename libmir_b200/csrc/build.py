@@ -34,7 +34,7 @@ LIBRARIES = {
     "core": {
         "sources": ["runtime.cu", "elementwise.cu", "qk_rope_store.cu", "attention_generic.cu", "gemm_f32.cu",
                     "sampling.cu", "executor.cu", "delta_rule.cu", "latent_attention.cu", "wkv.cu", "moe.cu",
-                    "retention.cu"],
+                    "retention.cu", "streams.cu", "qk_prepare.cu"],
         "link": [],
         "defines": [],
     },

@@ -200,8 +200,8 @@ struct Run {
     return mir_paged_attention_generic(step.bf16, step.qkv, width, step.mixed, layer.k_pages, layer.v_pages,
                                        group.block_table, group.table_width, step.row_of_token, step.positions,
                                        step.tokens, layer.page_size, layer.heads, layer.kv_heads, layer.head_dim,
-                                       layer.head_dim, layer.scale, layer.window, 0, 0, nullptr, nullptr, 0,
-                                       step.stream);
+                                       layer.head_dim, layer.scale, layer.window, 0, 0, nullptr, nullptr, 0, 0, 0.0f,
+                                       nullptr, 0, step.stream);
   }
 
   int feed_forward(const MirLayerDesc& layer, const MirNormDesc* upcoming) {

@@ -20,7 +20,8 @@ int mir_paged_attention_generic(int bf16, const void* q, long long q_token_strid
                                 const void* v_pages, const int* block_table, int table_width, const int* row_of_token,
                                 const int* positions, int tokens, int page_size, int heads, int kv_heads, int head_dim,
                                 int value_dim, float scale, int window, int keep_first, int value_row_width,
-                                const float* sinks, const void* gate, long long gate_stride, cudaStream_t stream);
+                                const float* sinks, const void* gate, long long gate_stride, int gate_per_head,
+                                float softcap, const float* rel_bias, int rel_rows, cudaStream_t stream);
 // gemm_f32.cu
 int mir_gemm_f32(const float* a, int lda, const float* w, int ldw, const float* bias, float* c, int ldc, int m, int n,
                  int k, float beta, cudaStream_t stream);

@@ -1,8 +1,10 @@
 // Kernels of a mixture of gated experts.  P = tokens * top pairs of (token, chosen expert); pair p = token * top + slot.
 //
-//   moe_route     per token, from the router's 32-bit logits (a product of the framework): sigmoid scores, choice among
-//                 the experts of the best groups by score + correction, weights = chosen scores / their sum * scale;
-//                 and the shared expert's gate
+//   moe_route     per token, from the router's 32-bit logits (a product of the framework): sigmoid scores (or a softmax
+//                 over all experts), choice among the experts of the best groups by score + correction (a group judged
+//                 by the sum of its two largest choice scores, or by its largest), weights = chosen scores / their sum
+//                 * scale; and the shared expert's gate.  The last experts of the router may be identity experts, which
+//                 have no weights: the sort leaves their pairs out, and moe_combine adds weight * the token's own input
 //   moe_sort      the pairs ordered by expert (a stable counting sort: a CTA per expert counts, one CTA scans, a CTA
 //                 per expert places), each expert's range, and the list of tiles (8 or 128 pairs of one expert)
 //                 that the grouped products walk over
@@ -45,7 +47,7 @@ __device__ __forceinline__ void warp_best(float& value, int& index, bool want_ma
 __global__ void moe_route_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ correction,
                                  int has_gate, int* __restrict__ ids, float* __restrict__ weights,
                                  float* __restrict__ shared_gate, int tokens, int experts, int top, int groups, int keep,
-                                 float scale) {
+                                 float scale, int softmax_scores, int group_by_max) {
   extern __shared__ float route_shared[];
   grid_launch_dependents();
   grid_dependency_wait();
@@ -56,8 +58,17 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, long long ld,
   float* choice = score + experts;
   float* group_score = choice + experts;
   const float* z = logits + (size_t)token * ld;
+  float softmax_top = 0.0f, softmax_inverse = 1.0f;
+  if (softmax_scores) {                                          // over all the router's experts, in 32-bit
+    float high = -FLT_MAX;
+    for (int e = lane; e < experts; e += 32) high = fmaxf(high, z[e]);
+    softmax_top = warp_max(high);
+    float sum = 0.0f;
+    for (int e = lane; e < experts; e += 32) sum += expf(z[e] - softmax_top);
+    softmax_inverse = 1.0f / warp_sum(sum);
+  }
   for (int e = lane; e < experts; e += 32) {
-    const float s = sigmoid_of(z[e]);
+    const float s = softmax_scores ? expf(z[e] - softmax_top) * softmax_inverse : sigmoid_of(z[e]);
     score[e] = s;
     choice[e] = correction != nullptr ? s + correction[e] : s;
   }
@@ -73,7 +84,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, long long ld,
         if (c > first) { second = first; first = c; }
         else if (c > second) second = c;
       }
-      group_score[g] = per_group > 1 ? first + second : first;
+      group_score[g] = (per_group > 1 && !group_by_max) ? first + second : first;
     }
     __syncwarp();
     // experts of all but the `keep` best groups cannot be chosen: their choice scores count as minus infinity
@@ -308,20 +319,30 @@ moe_grouped_kernel(const T* __restrict__ x, long long ldx, const int* __restrict
 }
 
 // One CTA per token: residual[t] += sum_s weights[t, s] * pair_rows[t * top + s] (+ shared_gate[t] * shared_rows[t], or
-// + shared_rows[t] without a gate), slots in their own order.
+// + shared_rows[t] without a gate), slots in their own order.  A slot whose expert is an identity expert (ids[pair] >=
+// real_experts) has no row: it adds weight * the token's own input (identity_rows, in the activations' type).
+// overwrite: the sum replaces residual[t] instead of being added to it.
+template <typename T>
 __global__ void moe_combine_kernel(float* __restrict__ residual, const float* __restrict__ pair_rows,
                                    const float* __restrict__ weights, const float* __restrict__ shared_rows,
-                                   const float* __restrict__ shared_gate, int width, int top) {
+                                   const float* __restrict__ shared_gate, int width, int top, int overwrite,
+                                   const int* __restrict__ ids, int real_experts, const T* __restrict__ identity_rows,
+                                   long long identity_stride) {
   grid_launch_dependents();
   grid_dependency_wait();
   const int token = blockIdx.x;
   const float gate = shared_rows != nullptr ? (shared_gate != nullptr ? shared_gate[token] : 1.0f) : 0.0f;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     float total = 0.0f;
-    for (int s = 0; s < top; ++s)
-      total = fmaf(weights[(size_t)token * top + s], pair_rows[((size_t)token * top + s) * width + c], total);
+    for (int s = 0; s < top; ++s) {
+      const size_t pair = (size_t)token * top + s;
+      const float row = (ids != nullptr && ids[pair] >= real_experts)
+                            ? to_float(identity_rows[(size_t)token * identity_stride + c])
+                            : pair_rows[pair * width + c];
+      total = fmaf(weights[pair], row, total);
+    }
     if (shared_rows != nullptr) total = fmaf(gate, shared_rows[(size_t)token * width + c], total);
-    residual[(size_t)token * width + c] += total;
+    residual[(size_t)token * width + c] = overwrite ? total : residual[(size_t)token * width + c] + total;
   }
 }
 
@@ -342,7 +363,7 @@ int launch_grouped(cudaStream_t stream, const void* x, long long ldx, const int*
 // logit behind them); correction [experts] (or null) 32-bit; ids, weights [tokens, top]; shared_gate [tokens].
 MIR_EXPORT int mir_moe_route(const float* logits, long long ld, const float* correction, int has_gate, int* ids,
                              float* weights, float* shared_gate, int tokens, int experts, int top, int groups, int keep,
-                             float scale, cudaStream_t stream) {
+                             float scale, int softmax_scores, int group_by_max, cudaStream_t stream) {
   if (tokens == 0) return MIR_OK;
   if (tokens < 0 || experts <= 0 || experts > kMaxExperts || top <= 0 || top > experts || groups <= 0 ||
       experts % groups || keep <= 0 || keep > groups || (long long)keep * (experts / groups) < top ||
@@ -354,7 +375,7 @@ MIR_EXPORT int mir_moe_route(const float* logits, long long ld, const float* cor
   const size_t smem = (size_t)kRouteWarps * (2 * experts + groups) * sizeof(float);
   return mir_launch("moe_route", moe_route_kernel, dim3((tokens + kRouteWarps - 1) / kRouteWarps), dim3(32, kRouteWarps),
                     smem, stream, 0, logits, ld, correction, has_gate, ids, weights, shared_gate, tokens, experts, top,
-                    groups, keep, scale);
+                    groups, keep, scale, softmax_scores, group_by_max);
 }
 
 // How many tiles of tile_pairs pairs there can be at most for `pairs` pairs over `experts` experts (`tiles` holds two
@@ -412,19 +433,22 @@ MIR_EXPORT int mir_moe_down(int bf16, const void* hidden, const int* order, cons
 
 // sorted[i, :] = h[order[i] / top, :]: the tokens' rows in the order of the sorted pairs (16-byte pieces).
 __global__ void moe_gather_rows_kernel(const uint4* __restrict__ h, long long ld_pieces, const int* __restrict__ order, int top,
-                                       uint4* __restrict__ sorted, int pieces, size_t total) {
+                                       uint4* __restrict__ sorted, int pieces, size_t total,
+                                       const int* __restrict__ sorted_count) {
   grid_launch_dependents();
   grid_dependency_wait();
   const size_t index = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (index >= total) return;
   const size_t row = index / pieces;
+  if (sorted_count != nullptr && row >= (size_t)sorted_count[0]) return;     // (pairs of identity experts are in no order)
   const int piece = (int)(index - row * pieces);
   sorted[index] = h[(size_t)(order[row] / top) * ld_pieces + piece];
 }
 
-// h [tokens, width] bfloat16 (row stride ld, both multiples of 8); sorted [pairs, width].
+// h [tokens, width] bfloat16 (row stride ld, both multiples of 8); sorted [pairs, width].  sorted_count (or null): one
+// number on the device, how many of the pairs the order holds (the pairs of identity experts are left out of it).
 MIR_EXPORT int mir_moe_gather_rows(const void* h, long long ld, const int* order, int top, void* sorted, int pairs,
-                                   int width, cudaStream_t stream) {
+                                   int width, const int* sorted_count, cudaStream_t stream) {
   if (pairs == 0) return MIR_OK;
   if (pairs < 0 || width <= 0 || width % 8 || ld % 8 || top <= 0) {
     mir_set_error("moe_gather_rows: rows of 16-byte pieces are needed (width %d, stride %lld)", width, ld);
@@ -433,13 +457,24 @@ MIR_EXPORT int mir_moe_gather_rows(const void* h, long long ld, const int* order
   const int pieces = width / 8;
   const size_t total = (size_t)pairs * pieces;
   return mir_launch("moe_gather_rows", moe_gather_rows_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, 0,
-                    (const uint4*)h, ld / 8, order, top, (uint4*)sorted, pieces, total);
+                    (const uint4*)h, ld / 8, order, top, (uint4*)sorted, pieces, total, sorted_count);
 }
 
 MIR_EXPORT int mir_moe_combine(float* residual, const float* pair_rows, const float* weights, const float* shared_rows,
-                               const float* shared_gate, int tokens, int width, int top, cudaStream_t stream) {
+                               const float* shared_gate, int tokens, int width, int top, int overwrite, const int* ids,
+                               int real_experts, int bf16, const void* identity_rows, long long identity_stride,
+                               cudaStream_t stream) {
   if (tokens == 0) return MIR_OK;
+  if (ids != nullptr && identity_rows == nullptr) {
+    mir_set_error("moe_combine: identity experts need the tokens' input rows");
+    return MIR_BAD_ARGUMENT;
+  }
   const int threads = width >= 1024 ? 256 : 128;
-  return mir_launch("moe_combine", moe_combine_kernel, dim3(tokens), dim3(threads), 0, stream, 0, residual, pair_rows,
-                    weights, shared_rows, shared_gate, width, top);
+  if (bf16)
+    return mir_launch("moe_combine", moe_combine_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, 0, residual,
+                      pair_rows, weights, shared_rows, shared_gate, width, top, overwrite, ids, real_experts,
+                      (const __nv_bfloat16*)identity_rows, identity_stride);
+  return mir_launch("moe_combine", moe_combine_kernel<float>, dim3(tokens), dim3(threads), 0, stream, 0, residual, pair_rows,
+                    weights, shared_rows, shared_gate, width, top, overwrite, ids, real_experts,
+                    (const float*)identity_rows, identity_stride);
 }

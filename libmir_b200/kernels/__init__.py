@@ -33,7 +33,15 @@ _SIGNATURES = {
                               c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_longlong, c_int, c_void_p],
         "mir_paged_attention_generic": [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                                        c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p],
+                                        c_int, c_int, c_void_p, c_void_p, c_longlong, c_int, c_float, c_void_p, c_int,
+                                        c_void_p],
+        "mir_qk_prepare": [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
+        "mir_layer_norm": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                           c_float, c_void_p],
+        "mir_streams_write": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "mir_streams_spread": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "mir_streams_sum": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "mir_embed_pairs": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                             c_longlong, c_longlong, c_float, c_void_p],
         "mir_gelu_tanh": [c_int, c_void_p, c_size_t, c_void_p],
@@ -68,7 +76,7 @@ _SIGNATURES = {
         "mir_wkv_scan": [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "mir_moe_route": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                          c_int, c_float, c_void_p],
+                          c_int, c_float, c_int, c_int, c_void_p],
         "mir_moe_tile_slots": [c_int, c_int, c_int],
         "mir_moe_sort": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                          c_void_p],
@@ -76,8 +84,9 @@ _SIGNATURES = {
                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "mir_moe_down": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                          c_int, c_int, c_void_p],
-        "mir_moe_gather_rows": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
-        "mir_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "mir_moe_gather_rows": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p],
+        "mir_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                            c_int, c_void_p, c_longlong, c_void_p],
         "mir_gemm_f32": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
                          c_void_p],
         "mir_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p,
@@ -824,11 +833,13 @@ def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, inv_freq: 
 # --------------------------------------------------------------------------- routed experts
 def moe_route(logits: torch.Tensor, correction: Optional[torch.Tensor], has_gate: bool, ids: torch.Tensor,
               weights: torch.Tensor, shared_gate: Optional[torch.Tensor], experts: int, top: int, groups: int, keep: int,
-              scale: float) -> None:
-    """Per token, from the router's 32-bit logits [tokens, >= experts (+ 1)]: scores = sigmoid(logits); the `top`
-    experts with the largest score + correction among the experts of the `keep` best of `groups` groups of neighbours
-    (a group's score: the sum of its two largest score + correction) -> ids [tokens, top]; weights [tokens, top] =
-    their scores / their sum * scale; with has_gate, shared_gate[t] = sigmoid(logits[t, experts])."""
+              scale: float, score: str = "sigmoid", group_score: str = "top2") -> None:
+    """Per token, from the router's 32-bit logits [tokens, >= experts (+ 1)]: scores = sigmoid(logits), or with
+    `score` "softmax" the softmax over the `experts` logits; the `top` experts with the largest score + correction
+    among the experts of the `keep` best of `groups` groups of neighbours (a group's score: the sum of its two largest
+    score + correction, or with `group_score` "max" the largest) -> ids [tokens, top]; weights [tokens, top] = their
+    scores / their sum * scale; with has_gate, shared_gate[t] = sigmoid(logits[t, experts])."""
+    _require(score in ("sigmoid", "softmax") and group_score in ("top2", "max"), "moe_route: unknown score rule")
     _cuda(logits, correction, ids, weights, shared_gate)
     tokens = logits.shape[0]
     _require(logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.shape[1] >= experts + int(has_gate)
@@ -840,7 +851,7 @@ def moe_route(logits: torch.Tensor, correction: Optional[torch.Tensor], has_gate
     lib = library("core")
     _check(lib, lib.mir_moe_route(logits.data_ptr(), logits.stride(0), _ptr(correction), int(has_gate), ids.data_ptr(),
                                   weights.data_ptr(), _ptr(shared_gate), tokens, experts, top, groups, keep, float(scale),
-                                  _stream()))
+                                  int(score == "softmax"), int(group_score == "max"), _stream()))
 
 
 class ExpertOrder:
@@ -902,7 +913,7 @@ def moe_gate_up(h: torch.Tensor, found: ExpertOrder, top: int, w_gate: torch.Ten
         ordered = alloc((found.pairs, width), torch.bfloat16)
         core = library("core")
         _check(core, core.mir_moe_gather_rows(h.data_ptr(), h.stride(0), found.order.data_ptr(), top, ordered.data_ptr(),
-                                              found.pairs, width, _stream()))
+                                              found.pairs, width, found.offsets[experts:].data_ptr(), _stream()))
         lib = library("bf16")
         _check(lib, lib.mir_gemm_tc_grouped_bf16(MODE_SWIGLU, ordered.data_ptr(), width, found.pairs, w_gate.data_ptr(),
                                                  experts, hidden.data_ptr(), inter, inter, width, found.tiles.data_ptr(),
@@ -939,10 +950,19 @@ def moe_down(hidden: torch.Tensor, found: ExpertOrder, w_down: torch.Tensor, pai
 
 
 def moe_combine(residual: torch.Tensor, pair_rows: torch.Tensor, weights: torch.Tensor,
-                shared_rows: Optional[torch.Tensor], shared_gate: Optional[torch.Tensor]) -> None:
+                shared_rows: Optional[torch.Tensor], shared_gate: Optional[torch.Tensor], overwrite: bool = False,
+                ids: Optional[torch.Tensor] = None, real_experts: int = 0,
+                identity_rows: Optional[torch.Tensor] = None) -> None:
     """residual[t] += sum_s weights[t, s] * pair_rows[t * top + s] + shared_gate[t] * shared_rows[t] (the gate 1 if
-    None; nothing of it without shared_rows); all 32-bit."""
-    _cuda(residual, pair_rows, weights, shared_rows, shared_gate)
+    None; nothing of it without shared_rows); all 32-bit.  `overwrite`: the sum replaces residual[t].  With `ids`
+    ([tokens, top] int32), a slot whose id is >= real_experts is an identity expert: it adds its weight times the
+    token's row of `identity_rows` (the experts' input, bfloat16 or float32) and has no row in pair_rows."""
+    _cuda(residual, pair_rows, weights, shared_rows, shared_gate, ids, identity_rows)
+    _require(ids is None or (ids.dtype == torch.int32 and ids.is_contiguous() and ids.shape == weights.shape
+                             and identity_rows is not None and identity_rows.stride(1) == 1
+                             and identity_rows.shape == residual.shape
+                             and identity_rows.dtype in (torch.bfloat16, torch.float32)),
+             "moe_combine: identity experts need int32 ids and the tokens' input rows")
     tokens, width = residual.shape
     top = weights.shape[1]
     _require(residual.dtype == torch.float32 and residual.is_contiguous() and pair_rows.dtype == torch.float32
@@ -954,7 +974,70 @@ def moe_combine(residual: torch.Tensor, pair_rows: torch.Tensor, weights: torch.
              "moe_combine: shapes or dtypes do not fit")
     lib = library("core")
     _check(lib, lib.mir_moe_combine(residual.data_ptr(), pair_rows.data_ptr(), weights.data_ptr(), _ptr(shared_rows),
-                                    _ptr(shared_gate), tokens, width, top, _stream()))
+                                    _ptr(shared_gate), tokens, width, top, int(overwrite), _ptr(ids), int(real_experts),
+                                    int(identity_rows is not None and identity_rows.dtype == torch.bfloat16),
+                                    _ptr(identity_rows) if ids is not None else None,
+                                    identity_rows.stride(0) if ids is not None else 0, _stream()))
+
+
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float, out: torch.Tensor,
+               rows: Optional[torch.Tensor] = None, read: Optional[torch.Tensor] = None) -> None:
+    """out[r] = (u - mean(u)) / sqrt(var(u) + eps) * weight + bias, var the mean of the squared deviations, everything
+    32-bit.  u is row rows[r] (or r) of x [tokens, width]; with `read` ([S] float32), x is a residual of S streams
+    [tokens, S, width] and u = sum_s read[s] x[token, s]."""
+    _cuda(x, weight, bias, out, rows, read)
+    n_rows, width = out.shape
+    _require(x.dtype == torch.float32 and x.is_contiguous() and weight.dtype == torch.float32 and weight.numel() == width
+             and (bias is None or (bias.dtype == torch.float32 and bias.numel() == width)) and out.is_contiguous()
+             and out.dtype in (torch.bfloat16, torch.float32), "layer_norm: bad arguments")
+    streams = 0
+    if read is not None:
+        _require(x.dim() == 3 and x.shape[2] == width and read.dtype == torch.float32 and read.numel() == x.shape[1],
+                 "layer_norm: a mix of streams needs x [tokens, streams, width] and float32 [streams] factors")
+        streams = x.shape[1]
+    else:
+        _require(x.dim() == 2 and x.shape[1] == width, "layer_norm: x must be [tokens, width]")
+    if rows is not None:
+        _require(rows.dtype == torch.int32 and rows.numel() == n_rows, "layer_norm: bad row index")
+    else:
+        _require(x.shape[0] >= n_rows, "layer_norm: fewer input rows than output rows")
+    lib = library("core")
+    _check(lib, lib.mir_layer_norm(_is_bf16(out), x.data_ptr(), streams, _ptr(read), weight.data_ptr(), _ptr(bias),
+                                   out.data_ptr(), _ptr(rows), n_rows, width, eps, _stream()))
+
+
+def streams_write(streams: torch.Tensor, branch: torch.Tensor, mix: torch.Tensor, write: torch.Tensor) -> None:
+    """A residual of S streams [tokens, S, width] takes a sublayer's result `branch` [tokens, width], in place and all
+    streams at once from the old ones: x_t <- sum_s mix[s, t] x_s + write[t] * branch.  All 32-bit."""
+    _cuda(streams, branch, mix, write)
+    tokens, count, width = streams.shape
+    _require(streams.dtype == torch.float32 and streams.is_contiguous() and branch.dtype == torch.float32
+             and branch.is_contiguous() and branch.shape == (tokens, width) and mix.dtype == torch.float32
+             and mix.is_contiguous() and mix.shape == (count, count) and write.dtype == torch.float32
+             and write.numel() == count, "streams_write: bad arguments")
+    lib = library("core")
+    _check(lib, lib.mir_streams_write(streams.data_ptr(), branch.data_ptr(), mix.data_ptr(), write.data_ptr(), tokens,
+                                      count, width, _stream()))
+
+
+def streams_spread(x: torch.Tensor, streams: torch.Tensor) -> None:
+    """Every stream of streams [tokens, S, width] becomes a copy of x [tokens, width] (32-bit)."""
+    _cuda(x, streams)
+    tokens, count, width = streams.shape
+    _require(x.dtype == torch.float32 and streams.dtype == torch.float32 and x.is_contiguous()
+             and streams.is_contiguous() and x.shape == (tokens, width), "streams_spread: bad arguments")
+    lib = library("core")
+    _check(lib, lib.mir_streams_spread(x.data_ptr(), streams.data_ptr(), tokens, count, width, _stream()))
+
+
+def streams_sum(streams: torch.Tensor, out: torch.Tensor) -> None:
+    """out [tokens, width] = the sum of the streams [tokens, S, width], streams in ascending order (32-bit)."""
+    _cuda(streams, out)
+    tokens, count, width = streams.shape
+    _require(out.dtype == torch.float32 and streams.dtype == torch.float32 and out.is_contiguous()
+             and streams.is_contiguous() and out.shape == (tokens, width), "streams_sum: bad arguments")
+    lib = library("core")
+    _check(lib, lib.mir_streams_sum(streams.data_ptr(), out.data_ptr(), tokens, count, width, _stream()))
 
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -1073,25 +1156,72 @@ def qk_rope_store(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Opti
                                       int(queries_only), _stream()))
 
 
+QK_NORM_SPANS = {None: 0, "head": 1, "projection": 2}
+
+
+def qk_prepare(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Optional[torch.Tensor],
+               inv_freq: Optional[torch.Tensor], q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+               k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], heads: int, kv_heads: int, head_dim: int,
+               value_dim: int, rotary_dim: int, eps: float, span: Optional[str], after_rotation: bool = False,
+               write_kv: bool = True) -> None:
+    """The q/k treatments that qk_rope_store does not know, on the packed rows in place for q, k and v into their
+    pages: an RMS norm of q and of k with `span` "head" (every head by itself; the weights, if any, are float32
+    [head_dim]), "projection" (q as a whole and k as a whole over all their heads; weights float32 [heads * head_dim]
+    and [kv_heads * head_dim]) or None; the half-split rotation of the first rotary_dim channels of every head;
+    `after_rotation`: the per-head norm follows the rotation.  The rows may be wider than q, k and v."""
+    _cuda(qkv, positions, slot_mapping, inv_freq, q_weight, k_weight, k_pages, v_pages)
+    _require(span in QK_NORM_SPANS, f"qk_prepare: unknown span {span!r}")
+    tokens = qkv.shape[0]
+    packed = (heads + kv_heads) * head_dim + kv_heads * value_dim
+    _require(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= packed and qkv.stride(0) >= qkv.shape[1],
+             "qk_prepare: bad qkv")
+    _require(positions.dtype == torch.int32 and positions.numel() >= tokens, "qk_prepare: bad positions")
+    if rotary_dim:
+        _require(inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2,
+                 "qk_prepare: the angle table must hold rotary_dim / 2 float32 values")
+    per = head_dim if span == "head" else 0
+    for weight, count in ((q_weight, heads), (k_weight, kv_heads)):
+        _require(weight is None or (span is not None and weight.dtype == torch.float32 and weight.is_contiguous()
+                                    and weight.numel() == (per or count * head_dim)),
+                 "qk_prepare: norm weights are float32, [head_dim] per head or [heads * head_dim] over the projection")
+    if write_kv:
+        _require(slot_mapping is not None and slot_mapping.dtype == torch.int32 and k_pages is not None
+                 and v_pages is not None and k_pages.dtype == qkv.dtype and v_pages.dtype == qkv.dtype,
+                 "qk_prepare: cache pages of the activations' dtype and a slot mapping are needed")
+    lib = library("core")
+    _check(lib, lib.mir_qk_prepare(_is_bf16(qkv), qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), _ptr(slot_mapping),
+                                   _ptr(inv_freq), _ptr(q_weight), _ptr(k_weight), _ptr(k_pages), _ptr(v_pages), tokens,
+                                   heads, kv_heads, head_dim, value_dim, rotary_dim, eps, QK_NORM_SPANS[span],
+                                   int(after_rotation), int(write_kv), _stream()))
+
+
 def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                             block_table: torch.Tensor, row_of_token: torch.Tensor, positions: torch.Tensor,
                             page_size: int, heads: int, kv_heads: int, head_dim: int, scale: float,
                             window: Optional[int], value_dim: Optional[int] = None, keep_first: int = 0,
                             values_in_keys: bool = False, sinks: Optional[torch.Tensor] = None,
-                            gate: Optional[torch.Tensor] = None) -> None:
+                            gate: Optional[torch.Tensor] = None, gate_per_head: bool = False,
+                            softcap: Optional[float] = None, distance_bias: Optional[torch.Tensor] = None) -> None:
     """out[t, h] = softmax over the visible cached keys of token t's request; q is read from the packed qkv rows.
     `value_dim`: width of a value head (head_dim if None); `keep_first`: with a window, the request's first keys
     that stay visible to every query; `values_in_keys`: a value is the first value_dim elements of its key (a cached
     latent that is read both ways) and v_pages is not looked at.  `sinks` (float32 [heads]): exp(sink_h) joins the
     denominator of head h's softmax.  `gate` ([tokens, heads * value_dim] view, unit column stride, out's dtype): the
-    result is multiplied by its sigmoid."""
+    result is multiplied by its sigmoid; with `gate_per_head` it is [tokens, heads], one number per head.  `softcap`:
+    score <- softcap * tanh(score / softcap) after the scale.  `distance_bias` (float32 [rows, heads]): row
+    min(query position - key position, rows - 1) is added to the scores after the cap."""
     if values_in_keys:
         v_pages = k_pages
-    _cuda(qkv, out, k_pages, v_pages, block_table, row_of_token, positions, sinks, gate)
+    _cuda(qkv, out, k_pages, v_pages, block_table, row_of_token, positions, sinks, gate, distance_bias)
     _require(sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == heads and sinks.is_contiguous()),
              "paged_attention: sinks are float32 [heads]")
-    _require(gate is None or (gate.dtype == out.dtype and gate.shape == out.shape and gate.stride(1) == 1),
-             "paged_attention: the gate has out's shape and dtype")
+    _require(gate is None or (gate.dtype == out.dtype and gate.stride(1) == 1
+                              and gate.shape == ((out.shape[0], heads) if gate_per_head else out.shape)),
+             "paged_attention: the gate has out's dtype and out's shape, or one column per head")
+    _require(distance_bias is None or (distance_bias.dtype == torch.float32 and distance_bias.is_contiguous()
+                                       and distance_bias.dim() == 2 and distance_bias.shape[1] == heads
+                                       and distance_bias.shape[0] > 0),
+             "paged_attention: the bias by distance is float32 [rows, heads]")
     tokens = out.shape[0]
     value_dim = head_dim if value_dim is None else value_dim
     _require(out.is_contiguous() and out.shape[1] == heads * value_dim and qkv.dtype == out.dtype
@@ -1103,7 +1233,9 @@ def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch
         _is_bf16(out), qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], row_of_token.data_ptr(), positions.data_ptr(), tokens,
         page_size, heads, kv_heads, head_dim, value_dim, scale, int(window or 0), int(keep_first or 0),
-        head_dim if values_in_keys else 0, _ptr(sinks), _ptr(gate), gate.stride(0) if gate is not None else 0, _stream()))
+        head_dim if values_in_keys else 0, _ptr(sinks), _ptr(gate), gate.stride(0) if gate is not None else 0,
+        int(gate_per_head), float(softcap or 0.0), _ptr(distance_bias),
+        distance_bias.shape[0] if distance_bias is not None else 0, _stream()))
 
 
 def _check_extras(what: str, sinks, gate, out: torch.Tensor, heads: int) -> None:
@@ -1331,9 +1463,13 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tens
         return False
     _require(rows.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16, "linear: x and weight must share a dtype")
     _require(out.dtype == torch.float32 or not accumulate, "linear: only a float32 output accumulates")
+    late_bias = None
     if bias is not None and bias.dtype != out.dtype:
-        _require(out.dtype == torch.float32 and accumulate, "linear: bias dtype must match out")
-        add_bias(out, bias)
+        _require(out.dtype == torch.float32 and (accumulate or out.is_contiguous()), "linear: bias dtype must match out")
+        if accumulate:
+            add_bias(out, bias)
+        else:
+            late_bias = bias           # a 32-bit result that replaces `out`: the bias is added behind the product
         bias = None
     stats, weighted, next_weight = None, None, None
     if sumsq_out is not None and weighted_out is not None and sumsq_out.numel() >= sumsq_tiles(n) * NORM_STAT_STRIDE:
@@ -1359,6 +1495,8 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tens
     if status == MIR_CANNOT_FOLD and lazy is not None:
         status = call(lazy.materialize(alloc), None)
     _check(lib, status)
+    if late_bias is not None:
+        add_bias(out, late_bias)
     return bool(wrote.value)
 
 

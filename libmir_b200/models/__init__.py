@@ -1,6 +1,6 @@
 """Architectures: each module registers its builder (config.json -> ModelSpec) by name."""
 
-from . import dalesun, dense_swiglu, doderax, zufotar  # noqa: F401
+from . import dalesun, dense_swiglu, doderax, gumazen, zufotar  # noqa: F401
 from .decoder import CacheEntryPlan, DecoderModel
 
 __all__ = ["CacheEntryPlan", "DecoderModel"]

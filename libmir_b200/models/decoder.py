@@ -44,6 +44,7 @@ class DecoderModel:
         self.loop_steps: Optional[torch.Tensor] = None          # [passes, hidden] 32-bit: what each pass of a loop adds
         self.head: Optional[torch.Tensor] = None
         self._runs_key, self._runs_list, self._native = None, [], {}
+        self.after_entry = None      # for inspection: called with (schedule index, streams) after every run of a layer
 
     # -- what the cache manager must provide ------------------------------------
     def cache_plan(self) -> List[CacheEntryPlan]:
@@ -162,6 +163,8 @@ class DecoderModel:
     def forward(self, ctx) -> torch.Tensor:
         """Run the tokens of the step; returns the 32-bit residual [T, H] after the last layer."""
         spec = self.spec
+        if spec.streams:
+            return self.forward_streams(ctx)
         residual = ctx.alloc((ctx.num_tokens, spec.hidden_size), torch.float32)
         if spec.embedding.pairs is not None:
             pairs = spec.embedding.pairs
@@ -195,6 +198,29 @@ class DecoderModel:
                                        and spec.schedule[index + 1].opens_pass is None)
             self.blocks[entry.layer].forward(ctx, ctx.cache_view(index), residual)
         return residual
+
+    def forward_streams(self, ctx) -> torch.Tensor:
+        """A residual kept as several streams [T, S, H]: every stream starts as the embedding's output, the blocks (of
+        the "streams" arrangement, run part by part) read and write all of them, and what the final norm gets is
+        their sum."""
+        spec = self.spec
+        if spec.embedding.pairs is not None or spec.loop is not None:
+            raise ValueError("a residual of several streams goes with a plain embedding and a loop without additions")
+        embedded = ctx.alloc((ctx.num_tokens, spec.hidden_size), torch.float32)
+        kernels.embed(self.embedding, ctx.tokens, embedded, spec.embedding.multiplier)
+        if self.embedding_norm is not None:
+            self.embedding_norm.forward(ctx, embedded, out=embedded)
+        streams = ctx.alloc((ctx.num_tokens, spec.streams, spec.hidden_size), torch.float32)
+        kernels.streams_spread(embedded, streams)
+        ctx.rounded_residual = None
+        ctx.norm_after_block = None
+        ctx.next_reads_residual = False
+        for index, entry in enumerate(spec.schedule):
+            self.blocks[entry.layer].forward(ctx, ctx.cache_view(index), streams)
+            if self.after_entry is not None:
+                self.after_entry(index, streams)
+        kernels.streams_sum(streams, embedded)
+        return embedded
 
     def _runs(self, ctx) -> list:
         """The schedule cut into runs: consecutive entries whose blocks the native executor takes form one run (one

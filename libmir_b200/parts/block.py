@@ -16,6 +16,11 @@ output_norm:  x += m * norm_1(mixer(x));  x += m * norm_2(feed_forward(x))
 Each branch reads the residual itself (cast to the engine's dtype) and its RESULT goes through the norm: the branch
 writes its result into a 32-bit buffer, and one kernel norms that buffer and adds m times it into the residual, so
 the norm and the residual sum are 32-bit.  m is LayerSpec.residual_scale.
+
+streams:  the residual is S copies x_1 .. x_S per token (hyper-connections).  For each of the two sublayers, with its
+stored mixing tensors in [S], mix [S, S] and out [S]:  u = sum_s in[s] x_s;  y = sublayer(norm(u));  then all streams
+at once from the old ones, x_t <- sum_s mix[s, t] x_s + out[t] y.  Everything outside the sublayer is 32-bit: the
+norm's kernel forms u on the way in, the sublayer leaves y in a 32-bit buffer, one kernel updates the streams.
 """
 
 from __future__ import annotations
@@ -23,7 +28,7 @@ from __future__ import annotations
 import torch
 
 from ..registry import build_part
-from .base import Block
+from .base import Block, Part
 
 
 class PreNormBlock(Block):
@@ -230,7 +235,75 @@ class OutputNormBlock(Block):
         ctx.residual_stats = None
 
 
-ARRANGEMENTS = {"pre_norm": PreNormBlock, "parallel": ParallelBlock, "output_norm": OutputNormBlock}
+class StreamMix(Part):
+    """The three small tensors by which one sublayer reads and writes a residual of several streams."""
+
+    graph_safe = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.read = self.write = self.mix = None
+
+    def parameters(self):
+        from ..config.spec import ParamSpec
+        s = self.spec.streams
+        return {"in": ParamSpec((s,), init="ones", store="float32"),
+                "out": ParamSpec((s,), init="ones", store="float32"),
+                "mix": ParamSpec((s, s), init="normal", store="float32", accept_transposed=False)}
+
+    def bind(self, tensors):
+        self.read, self.write, self.mix = (tensors[name].contiguous() for name in ("in", "out", "mix"))
+
+    def weight_bytes(self):
+        return sum(t.numel() * 4 for t in (self.read, self.write, self.mix))
+
+
+class StreamsBlock(Block):
+    """Pre-norm sublayers on a residual of several streams [tokens, S, width]: each reads a mix of the streams through
+    its norm and writes its result into all of them."""
+
+    SLOTS = ("mixer_norm", "mixer", "feed_forward_norm", "feed_forward", "mixer_streams", "feed_forward_streams")
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        for slot in self.SLOTS:
+            setattr(self, slot, build_part(getattr(spec, slot), env))
+        if self.mixer_norm is None or self.mixer_streams is None or \
+                (self.feed_forward is not None and (self.feed_forward_norm is None or self.feed_forward_streams is None)):
+            raise ValueError("the streams arrangement takes a norm and mixing tensors for every sublayer")
+        from .norm import LayerNorm
+        if any(norm is not None and type(norm) is not LayerNorm for norm in (self.mixer_norm, self.feed_forward_norm)):
+            raise ValueError("the streams arrangement reads through a layer norm (the norm whose kernel mixes the streams)")
+
+    def parts(self):
+        return [(slot, getattr(self, slot)) for slot in self.SLOTS if getattr(self, slot) is not None]
+
+    def cache_requirement(self):
+        return self.mixer.cache_requirement()
+
+    def forward(self, ctx, cache, residual):
+        from .. import kernels
+        ctx.upcoming_norm = None             # the products' results go through the streams' update, not into a norm
+        ctx.residual_stats = None
+        tokens, _, width = residual.shape
+        result = ctx.alloc((tokens, width), torch.float32)
+        x = self._read(ctx, self.mixer_norm, self.mixer_streams, residual)
+        self.mixer.forward(ctx, cache, x, result, overwrite=True)
+        kernels.streams_write(residual, result, self.mixer_streams.mix, self.mixer_streams.write)
+        if self.feed_forward is not None:
+            x = self._read(ctx, self.feed_forward_norm, self.feed_forward_streams, residual)
+            self.feed_forward.forward(ctx, x, result, overwrite=True)
+            kernels.streams_write(residual, result, self.feed_forward_streams.mix, self.feed_forward_streams.write)
+        ctx.residual_stats = None
+
+    @staticmethod
+    def _read(ctx, norm, streams, residual):
+        """norm(sum_s in[s] x_s) in the engine dtype; the norm's kernel forms the mix on the way in."""
+        return norm.forward(ctx, residual, read=streams.read)
+
+
+ARRANGEMENTS = {"pre_norm": PreNormBlock, "parallel": ParallelBlock, "output_norm": OutputNormBlock,
+                "streams": StreamsBlock}
 
 
 def build_block(layer_spec, env):

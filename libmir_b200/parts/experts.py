@@ -9,6 +9,10 @@ With h the feed-forward's input, E experts of which each token uses `top`:
     chosen = the `top` experts with the largest choice scores;  weight = s[chosen] / (sum of them + 1e-20) * scale
     out = sum over chosen of weight * expert(h)    expert(h) = W_down (silu(W_gate h) * (W_up h))
         + sigmoid(w_sg . h) * shared(h)            one number per token gates the shared expert, if there is one
+Other forms from the spec: s = softmax(W_router h) over all the router's outputs; a group's score = its largest choice
+score; the last `identity` outputs of the router are identity experts, which have no tensors and whose result is h
+itself (they take part in scores, groups and choice; the ordered pairs leave them out, and the kernel that adds the
+weighted rows reads h for them); a shared expert without a gate.
 Everything runs on the device without a count ever being read back (csrc/moe.cu): the (token, expert) pairs are
 ordered by expert, two grouped products run over the ordered pairs with each pair's expert's weights (in bfloat16 on
 tensor cores: the tcgen05 product of csrc/gemm_tc.cu on row tiles from a list on the device; in float32 as 32-bit
@@ -31,10 +35,13 @@ class RoutedExperts(FeedForward):
     def __init__(self, spec, env):
         super().__init__(spec, env)
         s = spec
-        if s.experts <= 0 or not 0 < s.top <= s.experts or s.groups <= 0 or s.experts % s.groups \
-                or not 0 < s.keep_groups <= s.groups or s.keep_groups * (s.experts // s.groups) < s.top:
-            raise ValueError(f"routed experts: {s.top} of {s.experts} experts cannot be chosen from {s.keep_groups} of "
+        self.routed = s.experts + s.identity          # the router's outputs: experts with weights, then identity experts
+        if s.experts <= 0 or s.identity < 0 or not 0 < s.top <= self.routed or s.groups <= 0 or self.routed % s.groups \
+                or not 0 < s.keep_groups <= s.groups or s.keep_groups * (self.routed // s.groups) < s.top:
+            raise ValueError(f"routed experts: {s.top} of {self.routed} experts cannot be chosen from {s.keep_groups} of "
                              f"{s.groups} groups")
+        if s.score not in ("sigmoid", "softmax") or s.group_score not in ("top2", "max"):
+            raise ValueError(f"routed experts: unknown score rule {s.score!r} / {s.group_score!r}")
         self.router = self.correction = self.w_gate = self.w_up = self.w_down = None
         self.shared_gate_up = self.shared_down = None
         self.shared_gate = False
@@ -42,9 +49,9 @@ class RoutedExperts(FeedForward):
     def parameters(self):
         s = self.spec
         matrix = lambda rows, columns: ParamSpec((rows, columns), accept_transposed=False)
-        table = {"router": matrix(s.experts, s.hidden_size)}
+        table = {"router": matrix(self.routed, s.hidden_size)}
         if s.correction:
-            table["correction"] = ParamSpec((s.experts,), init="zeros", store="float32")
+            table["correction"] = ParamSpec((self.routed,), init="zeros", store="float32")
         for expert in range(s.experts):
             table[f"e{expert}.gate"] = matrix(s.expert_size, s.hidden_size)
             table[f"e{expert}.up"] = matrix(s.expert_size, s.hidden_size)
@@ -61,7 +68,7 @@ class RoutedExperts(FeedForward):
         s = self.spec
         # the router's rows and, behind them, the shared expert's gate row: one product gives every 32-bit logit
         rows = [tensors["router"]] + ([tensors["shared.sg"].reshape(1, -1)] if s.shared_size and s.shared_gate else [])
-        padding = -(s.experts + len(rows) - 1) % 8
+        padding = -(self.routed + len(rows) - 1) % 8
         if padding:
             rows.append(torch.zeros((padding, s.hidden_size), dtype=tensors["router"].dtype, device=tensors["router"].device))
         self.router = torch.cat(rows, dim=0).contiguous()
@@ -82,7 +89,9 @@ class RoutedExperts(FeedForward):
         tensors = (self.router, self.w_gate, self.w_up, self.w_down, self.shared_gate_up, self.shared_down)
         return sum(t.numel() * t.element_size() for t in tensors if t is not None)
 
-    def forward(self, ctx, x, residual):
+    def forward(self, ctx, x, residual, overwrite=False):
+        """residual += the experts' weighted results; with `overwrite` they replace `residual` (a 32-bit buffer of an
+        arrangement that takes the branch's result by itself)."""
         s = self.spec
         tokens = x.shape[0]
         dtype = self.env.dtype
@@ -91,8 +100,8 @@ class RoutedExperts(FeedForward):
         gate = ctx.alloc((tokens,), torch.float32) if self.shared_gate else None
         logits = ctx.alloc((tokens, self.router.shape[0]), torch.float32)
         kernels.linear(x, self.router, logits, alloc=ctx.alloc)       # 32-bit accumulation and result
-        kernels.moe_route(logits, self.correction, self.shared_gate, ids, weights, gate, s.experts, s.top, s.groups,
-                          s.keep_groups, s.scale)
+        kernels.moe_route(logits, self.correction, self.shared_gate, ids, weights, gate, self.routed, s.top, s.groups,
+                          s.keep_groups, s.scale, score=s.score, group_score=s.group_score)
         found = kernels.moe_sort(ids, s.experts, ctx.alloc, kernels.expert_tile_pairs(dtype, s.hidden_size, s.expert_size))
         hidden = ctx.alloc((tokens * s.top, s.expert_size), dtype)
         kernels.moe_gate_up(x, found, s.top, self.w_gate, self.w_up, hidden, ctx.alloc)
@@ -104,5 +113,7 @@ class RoutedExperts(FeedForward):
             kernels.gate_up_silu(x, self.shared_gate_up, shared_hidden, ctx.alloc)
             shared_rows = ctx.alloc((tokens, s.hidden_size), torch.float32)
             kernels.linear(shared_hidden, self.shared_down, shared_rows, alloc=ctx.alloc)
-        kernels.moe_combine(residual, pair_rows, weights, shared_rows, gate)
+        kernels.moe_combine(residual, pair_rows, weights, shared_rows, gate, overwrite=overwrite,
+                            ids=ids if s.identity else None, real_experts=s.experts,
+                            identity_rows=x if s.identity else None)
         ctx.residual_stats = None
