@@ -228,7 +228,7 @@ constexpr int kDecodeMaxTiles = kDecodeMaxPartition / (kDecodeWarps * kDecodeTil
 // Per 16-key tile a warp computes S = Q K^T (heads on the M side, 8 real rows), the softmax update of its
 // 8 heads, and O^T += V^T P^T (head_dim on the M side, heads on the N side: the padding rows cost nothing
 // here, and P^T in the layout the product wants is exactly the layout S came out in).
-template <int D, int kDecodeStages>
+template <int D, int kDecodeStages, bool SCORED>
 __global__ void __launch_bounds__(kDecodeWarps * 32)
 decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16* __restrict__ k_pages,
                         const bf16* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
@@ -346,6 +346,13 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
     float s[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
     scores<D, 2>(s, qa, k_tile, lane);
     float v00 = s[0][0] * scale_log2, v01 = s[0][1] * scale_log2, v10 = s[1][0] * scale_log2, v11 = s[1][1] * scale_log2;
+    if (SCORED) {                                               // a cap and a bias by distance, in 32-bit
+      const int distance = position - (tile + quad * 2), head = head0 + group_row;
+      v00 = modified_score(extras, v00, distance, head);
+      v01 = modified_score(extras, v01, distance - 1, head);
+      v10 = modified_score(extras, v10, distance - 8, head);
+      v11 = modified_score(extras, v11, distance - 9, head);
+    }
     if (kept_tile) {                                            // of a kept tile, the kept keys are seen
       const int key = tile + quad * 2;
       if (key >= kept_end) v00 = -INFINITY;
@@ -607,7 +614,7 @@ constexpr int kPrefillWarps = 4;
 constexpr int kQueryTile = kPrefillWarps * 16;     // 64 tokens per CTA
 constexpr int kKeyTile = 64;
 
-template <int D>
+template <int D, bool SCORED>
 __global__ void __launch_bounds__(kPrefillWarps * 32, 3)
 prefill_attention_kernel(const bf16* __restrict__ q, size_t q_stride, bf16* __restrict__ out,
                          const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
@@ -719,7 +726,10 @@ prefill_attention_kernel(const bf16* __restrict__ q, size_t q_stride, bf16* __re
             const int pos = (e < 2) ? pos0 : pos1;
             visible = key <= pos && (window <= 0 || key > pos - window || key < keep_first);
           }
-          s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
+          float value = s[nt][e] * scale_log2;
+          if (SCORED && visible)                               // a cap and a bias by distance, in 32-bit
+            value = modified_score(extras, value, ((e < 2) ? pos0 : pos1) - (key0 + nt * 8 + c + (e & 1)), head);
+          s[nt][e] = visible ? value : -INFINITY;
         }
       uint32_t pa[NT / 2][4];
       softmax<D, NT>(s, m, l, o, pa);
@@ -788,16 +798,25 @@ int launch_decode_staged(const bf16* q, size_t q_stride, bf16* out, const bf16* 
   const size_t combine = (size_t)kDecodeWarps * kDecodeHeads * (D + 2) * sizeof(float);
   const size_t smem = pipeline > combine ? pipeline : combine;
   static bool smem_set = false;                               // per head size and depth: this function is a template
-  int status = set_smem(decode_attention_kernel<D, STAGES>, smem, "decode_attention", smem_set);
+  static bool smem_set_scored = false;
+  const bool scored = extras.softcap > 0.0f || extras.rel_bias != nullptr;
+  int status = scored ? set_smem(decode_attention_kernel<D, STAGES, true>, smem, "decode_attention", smem_set_scored)
+                      : set_smem(decode_attention_kernel<D, STAGES, false>, smem, "decode_attention", smem_set);
   if (status != MIR_OK) return status;
   const int group = heads / kv_heads;
   const int units = kv_heads * ((group + kDecodeHeads - 1) / kDecodeHeads);
   const dim3 grid = rows <= 4 ? dim3(rows, units, num_partitions) : dim3(num_partitions, units, rows);
-  status = mir_launch_with(mir_pdl_for_streaming(), "decode_attention", decode_attention_kernel<D, STAGES>, grid,
-                           dim3(kDecodeWarps * 32), smem, stream, 0, q, q_stride, k_pages, v_pages, block_table,
-                           table_width, positions, page_size, heads, kv_heads, scale * 1.4426950408889634f, window,
-                           partition, num_partitions, rows <= 4 ? 1 : 0, partial_o, partial_ml, out, keep_first,
-                           virtual_positions, extras);
+  status = scored
+      ? mir_launch_with(mir_pdl_for_streaming(), "decode_attention", decode_attention_kernel<D, STAGES, true>, grid,
+                        dim3(kDecodeWarps * 32), smem, stream, 0, q, q_stride, k_pages, v_pages, block_table,
+                        table_width, positions, page_size, heads, kv_heads, scale * 1.4426950408889634f, window,
+                        partition, num_partitions, rows <= 4 ? 1 : 0, partial_o, partial_ml, out, keep_first,
+                        virtual_positions, extras)
+      : mir_launch_with(mir_pdl_for_streaming(), "decode_attention", decode_attention_kernel<D, STAGES, false>, grid,
+                        dim3(kDecodeWarps * 32), smem, stream, 0, q, q_stride, k_pages, v_pages, block_table,
+                        table_width, positions, page_size, heads, kv_heads, scale * 1.4426950408889634f, window,
+                        partition, num_partitions, rows <= 4 ? 1 : 0, partial_o, partial_ml, out, keep_first,
+                        virtual_positions, extras);
   if (status != MIR_OK || num_partitions == 1) return status;
   if (keep_first > 0 && window > 0)      // the partitions were counted in the kernel's own numbering of the visible keys
     return launch_merge<D>(partial_o, partial_ml, virtual_positions, rows, heads, 0, partition, num_partitions, out, stream,
@@ -831,14 +850,22 @@ int launch_prefill(const bf16* q, size_t q_stride, bf16* out, const bf16* k_page
                    int keep_first, cudaStream_t stream, AttentionExtras extras = {}) {
   const size_t smem = (size_t)2 * 2 * kKeyTile * (D + 8) * sizeof(bf16);
   static bool smem_set = false;
-  int status = set_smem(prefill_attention_kernel<D>, smem, "prefill_attention", smem_set);
+  static bool smem_set_scored = false;
+  const bool scored = extras.softcap > 0.0f || extras.rel_bias != nullptr;
+  int status = scored ? set_smem(prefill_attention_kernel<D, true>, smem, "prefill_attention", smem_set_scored)
+                      : set_smem(prefill_attention_kernel<D, false>, smem, "prefill_attention", smem_set);
   if (status != MIR_OK) return status;
   const int tiles = (tokens + kQueryTile - 1) / kQueryTile + num_rows;   // an upper bound; spare CTAs return
   if (tiles > 65535) {
     mir_set_error("prefill_attention: %d tokens in %d rows are more than one launch takes", tokens, num_rows);
     return MIR_BAD_ARGUMENT;
   }
-  return mir_launch("prefill_attention", prefill_attention_kernel<D>, dim3(heads, tiles), dim3(kPrefillWarps * 32),
+  if (scored)
+    return mir_launch("prefill_attention", prefill_attention_kernel<D, true>, dim3(heads, tiles), dim3(kPrefillWarps * 32),
+                      smem, stream, 0, q, q_stride, out, k_pages, v_pages, block_table, table_width, query_starts,
+                      context_lens, num_rows, page_size, heads, kv_heads, scale * 1.4426950408889634f, window,
+                      keep_first, extras);
+  return mir_launch("prefill_attention", prefill_attention_kernel<D, false>, dim3(heads, tiles), dim3(kPrefillWarps * 32),
                     smem, stream, 0, q, q_stride, out, k_pages, v_pages, block_table, table_width, query_starts,
                     context_lens, num_rows, page_size, heads, kv_heads, scale * 1.4426950408889634f, window,
                     keep_first, extras);
@@ -932,15 +959,14 @@ MIR_EXPORT int mir_decode_attention_bf16(const void* q, long long q_stride, void
 // The same with a window's kept first keys (keep_first; virtual_positions: rows ints of scratch for the merge), and
 // with what AttentionExtras describes: sinks [heads] 32-bit or null; gate rows [token][heads * head_dim] with a row
 // stride in elements, or null.
-MIR_EXPORT int mir_decode_attention_extra_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
-                                               const void* v_pages, const int* block_table, int table_width,
-                                               const int* positions, int rows, int page_size, int heads, int kv_heads,
-                                               int head_dim, float scale, int window, int partition,
-                                               int num_partitions, float* scratch, long long scratch_floats,
-                                               cudaStream_t stream, int keep_first, int* virtual_positions,
-                                               const float* sinks, const void* gate, long long gate_stride) {
+static int decode_attention_with(const void* q, long long q_stride, void* out, const void* k_pages,
+                                 const void* v_pages, const int* block_table, int table_width,
+                                 const int* positions, int rows, int page_size, int heads, int kv_heads,
+                                 int head_dim, float scale, int window, int partition,
+                                 int num_partitions, float* scratch, long long scratch_floats,
+                                 cudaStream_t stream, int keep_first, int* virtual_positions,
+                                 const AttentionExtras& extras) {
   if (rows == 0) return MIR_OK;
-  const AttentionExtras extras{sinks, (const bf16*)gate, gate_stride};
   if (keep_first < 0 || (keep_first > 0 && window > 0 && virtual_positions == nullptr)) {
     mir_set_error("decode_attention: kept first keys need room for one number per row");
     return MIR_BAD_ARGUMENT;
@@ -969,6 +995,37 @@ MIR_EXPORT int mir_decode_attention_extra_bf16(const void* q, long long q_stride
                             extras);
 }
 
+MIR_EXPORT int mir_decode_attention_extra_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                               const void* v_pages, const int* block_table, int table_width,
+                                               const int* positions, int rows, int page_size, int heads, int kv_heads,
+                                               int head_dim, float scale, int window, int partition,
+                                               int num_partitions, float* scratch, long long scratch_floats,
+                                               cudaStream_t stream, int keep_first, int* virtual_positions,
+                                               const float* sinks, const void* gate, long long gate_stride) {
+  const AttentionExtras extras{sinks, (const bf16*)gate, gate_stride};
+  return decode_attention_with(q, q_stride, out, k_pages, v_pages, block_table, table_width, positions, rows, page_size,
+                               heads, kv_heads, head_dim, scale, window, partition, num_partitions, scratch,
+                               scratch_floats, stream, keep_first, virtual_positions, extras);
+}
+
+// The same with scores that are capped (softcap > 0) and biased by distance (rel_bias [rel_rows, heads] 32-bit or
+// null), and with a gate of one column per head (gate_per_head).
+MIR_EXPORT int mir_decode_attention_scored_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                                const void* v_pages, const int* block_table, int table_width,
+                                                const int* positions, int rows, int page_size, int heads, int kv_heads,
+                                                int head_dim, float scale, int window, int partition,
+                                                int num_partitions, float* scratch, long long scratch_floats,
+                                                cudaStream_t stream, const float* sinks, const void* gate,
+                                                long long gate_stride, int gate_per_head, float softcap,
+                                                const float* rel_bias, int rel_rows) {
+  if (rel_bias != nullptr && rel_rows <= 0) { mir_set_error("decode_attention: a bias by distance needs rows"); return MIR_BAD_ARGUMENT; }
+  const AttentionExtras extras{sinks, (const bf16*)gate, gate_stride, gate_per_head ? head_dim : 0, softcap, rel_bias,
+                               rel_rows, heads};
+  return decode_attention_with(q, q_stride, out, k_pages, v_pages, block_table, table_width, positions, rows, page_size,
+                               heads, kv_heads, head_dim, scale, window, partition, num_partitions, scratch,
+                               scratch_floats, stream, 0, nullptr, extras);
+}
+
 MIR_EXPORT int mir_decode_attention_kept_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
                                               const void* v_pages, const int* block_table, int table_width,
                                               const int* positions, int rows, int page_size, int heads, int kv_heads,
@@ -986,14 +1043,13 @@ MIR_EXPORT int mir_decode_attention_kept_bf16(const void* q, long long q_stride,
 // keep_first: with a window, the first keys of every request that stay visible to all its later queries.
 // sinks, gate, gate_stride: what AttentionExtras describes (null for none); gate rows are indexed by the token's place
 // in the packed batch.
-MIR_EXPORT int mir_prefill_attention_extra_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
-                                                const void* v_pages, const int* block_table, int table_width,
-                                                const int* query_starts, const int* context_lens, int num_rows,
-                                                int tokens, int page_size, int heads, int kv_heads, int head_dim,
-                                                float scale, int window, int keep_first, cudaStream_t stream,
-                                                const float* sinks, const void* gate, long long gate_stride) {
+static int prefill_attention_with(const void* q, long long q_stride, void* out, const void* k_pages,
+                                  const void* v_pages, const int* block_table, int table_width,
+                                  const int* query_starts, const int* context_lens, int num_rows,
+                                  int tokens, int page_size, int heads, int kv_heads, int head_dim,
+                                  float scale, int window, int keep_first, cudaStream_t stream,
+                                  const AttentionExtras& extras) {
   if (tokens == 0 || num_rows == 0) return MIR_OK;
-  const AttentionExtras extras{sinks, (const bf16*)gate, gate_stride};
   if (bad_common("prefill_attention", heads, kv_heads, head_dim, page_size, table_width, window) || keep_first < 0)
     return MIR_BAD_ARGUMENT;
   if (tokens < 0 || num_rows < 0) {
@@ -1007,6 +1063,33 @@ MIR_EXPORT int mir_prefill_attention_extra_bf16(const void* q, long long q_strid
   return launch_prefill<128>((const bf16*)q, (size_t)q_stride, (bf16*)out, (const bf16*)k_pages, (const bf16*)v_pages,
                              block_table, table_width, query_starts, context_lens, num_rows, tokens, page_size, heads,
                              kv_heads, scale, window, keep_first, stream, extras);
+}
+
+MIR_EXPORT int mir_prefill_attention_extra_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                                const void* v_pages, const int* block_table, int table_width,
+                                                const int* query_starts, const int* context_lens, int num_rows,
+                                                int tokens, int page_size, int heads, int kv_heads, int head_dim,
+                                                float scale, int window, int keep_first, cudaStream_t stream,
+                                                const float* sinks, const void* gate, long long gate_stride) {
+  const AttentionExtras extras{sinks, (const bf16*)gate, gate_stride};
+  return prefill_attention_with(q, q_stride, out, k_pages, v_pages, block_table, table_width, query_starts, context_lens,
+                                num_rows, tokens, page_size, heads, kv_heads, head_dim, scale, window, keep_first, stream,
+                                extras);
+}
+
+// The same with capped and biased scores and a gate of one column per head, as mir_decode_attention_scored_bf16.
+MIR_EXPORT int mir_prefill_attention_scored_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                                 const void* v_pages, const int* block_table, int table_width,
+                                                 const int* query_starts, const int* context_lens, int num_rows,
+                                                 int tokens, int page_size, int heads, int kv_heads, int head_dim,
+                                                 float scale, int window, cudaStream_t stream, const float* sinks,
+                                                 const void* gate, long long gate_stride, int gate_per_head,
+                                                 float softcap, const float* rel_bias, int rel_rows) {
+  if (rel_bias != nullptr && rel_rows <= 0) { mir_set_error("prefill_attention: a bias by distance needs rows"); return MIR_BAD_ARGUMENT; }
+  const AttentionExtras extras{sinks, (const bf16*)gate, gate_stride, gate_per_head ? head_dim : 0, softcap, rel_bias,
+                               rel_rows, heads};
+  return prefill_attention_with(q, q_stride, out, k_pages, v_pages, block_table, table_width, query_starts, context_lens,
+                                num_rows, tokens, page_size, heads, kv_heads, head_dim, scale, window, 0, stream, extras);
 }
 
 MIR_EXPORT int mir_prefill_attention_kept_bf16(const void* q, long long q_stride, void* out, const void* k_pages,

@@ -118,6 +118,13 @@ struct AttentionExtras {
   const float* sinks = nullptr;
   const __nv_bfloat16* gate = nullptr;
   long long gate_stride = 0;
+  // gate_head_width > 0: a gate row holds one number per head (of that many result columns) instead of one per column.
+  int gate_head_width = 0;
+  // softcap > 0: score <- softcap * tanh(score / softcap) after the scale.  rel_bias [rel_rows, rel_heads] 32-bit (or
+  // null): the row min(query position - key position, rel_rows - 1) of the head is added after the cap.
+  float softcap = 0.0f;
+  const float* rel_bias = nullptr;
+  int rel_rows = 0, rel_heads = 0;
 };
 // The sink's share of a denominator whose terms are exp2(score * log2 e - reference).
 __device__ __forceinline__ float sink_term(const AttentionExtras& extras, int head, float reference) {
@@ -125,7 +132,19 @@ __device__ __forceinline__ float sink_term(const AttentionExtras& extras, int he
 }
 __device__ __forceinline__ float gate_factor(const AttentionExtras& extras, size_t token, size_t column) {
   if (extras.gate == nullptr) return 1.0f;
+  if (extras.gate_head_width > 0) column /= (size_t)extras.gate_head_width;
   return 1.0f / (1.0f + __expf(-__bfloat162float(extras.gate[token * (size_t)extras.gate_stride + column])));
+}
+__device__ __forceinline__ bool scores_modified(const AttentionExtras& extras) {
+  return extras.softcap > 0.0f || extras.rel_bias != nullptr;
+}
+// A score that is already scaled and in units of log2 e (the tile kernels' form), capped and biased in 32-bit.
+__device__ __forceinline__ float modified_score(const AttentionExtras& extras, float score_log2, int distance, int head) {
+  float x = score_log2 * 0.6931471805599453f;
+  if (extras.softcap > 0.0f) x = extras.softcap * tanhf(x / extras.softcap);
+  if (extras.rel_bias != nullptr)
+    x += extras.rel_bias[(size_t)min(max(distance, 0), extras.rel_rows - 1) * extras.rel_heads + min(head, extras.rel_heads - 1)];
+  return x * 1.4426950408889634f;
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

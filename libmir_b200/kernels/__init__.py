@@ -105,6 +105,14 @@ _SIGNATURES = {
         "mir_decode_attention_extra_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                             c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p,
                                             c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong],
+        "mir_decode_attention_scored_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                             c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p,
+                                             c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_float,
+                                             c_void_p, c_int],
+        "mir_prefill_attention_scored_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                              c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_float, c_void_p,
+                                              c_int],
         "mir_decode_attention_paged_extra_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong,
                                                   c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                                   c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p,
@@ -1238,11 +1246,17 @@ def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch
         distance_bias.shape[0] if distance_bias is not None else 0, _stream()))
 
 
-def _check_extras(what: str, sinks, gate, out: torch.Tensor, heads: int) -> None:
+def _check_extras(what: str, sinks, gate, out: torch.Tensor, heads: int, gate_per_head: bool = False,
+                  distance_bias=None) -> None:
     _require(sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == heads and sinks.is_contiguous()),
              f"{what}: sinks are float32 [heads]")
-    _require(gate is None or (gate.dtype == out.dtype and gate.shape == out.shape and gate.stride(1) == 1),
-             f"{what}: the gate has out's shape and dtype")
+    _require(gate is None or (gate.dtype == out.dtype and gate.stride(1) == 1
+                              and gate.shape == ((out.shape[0], heads) if gate_per_head else out.shape)),
+             f"{what}: the gate has out's dtype and out's shape, or one column per head")
+    _require(distance_bias is None or (distance_bias.dtype == torch.float32 and distance_bias.is_contiguous()
+                                       and distance_bias.dim() == 2 and distance_bias.shape[1] == heads
+                                       and distance_bias.shape[0] > 0),
+             f"{what}: the bias by distance is float32 [rows, heads]")
 
 
 FAST_HEAD_DIMS = (64, 128)      # what the tensor-core attention kernels take; other sizes use the reference kernel
@@ -1279,15 +1293,18 @@ def decode_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor
                      head_dim: int, scale: float, window: Optional[int], partition: int, num_partitions: int,
                      scratch: Optional[torch.Tensor], keep_first: int = 0,
                      numbering: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None,
-                     gate: Optional[torch.Tensor] = None) -> None:
+                     gate: Optional[torch.Tensor] = None, gate_per_head: bool = False, softcap: Optional[float] = None,
+                     distance_bias: Optional[torch.Tensor] = None) -> None:
     """bf16 split-KV attention for a batch of single tokens (row r of qkv belongs to request row r).  `keep_first`:
     with a window, the request's first keys that stay visible; the mma.sync kernel then walks over the kept keys and
     the window's as one run, and `numbering` (int32 [rows]) is scratch for the merge.  `sinks`, `gate`: as
     paged_attention_generic takes them (the kernel that writes a row's final result, the attention kernel or the
-    merge of its partitions, adds the sink's term and applies the gate)."""
-    _cuda(qkv, out, k_pages, v_pages, block_table, positions, scratch, sinks, gate)
+    merge of its partitions, adds the sink's term and applies the gate).  `gate_per_head`, `softcap`, `distance_bias`:
+    as paged_attention_generic takes them; with any of them the mma.sync kernel runs (the scores are capped and
+    biased in 32-bit before the softmax; partitions of decode_attention_kept_plan)."""
+    _cuda(qkv, out, k_pages, v_pages, block_table, positions, scratch, sinks, gate, distance_bias)
     rows = out.shape[0]
-    _check_extras("decode_attention", sinks, gate, out, heads)
+    _check_extras("decode_attention", sinks, gate, out, heads, gate_per_head, distance_bias)
     gate_args = (_ptr(sinks), _ptr(gate), gate.stride(0) if gate is not None else 0)
     _require(qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16
              and v_pages.dtype == torch.bfloat16 and out.is_contiguous() and out.shape[1] == heads * head_dim,
@@ -1298,6 +1315,15 @@ def decode_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor
     lib = library("bf16")
     _require(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.shape[0] == v_pages.shape[0],
              "decode_attention: the cache tensors must be contiguous [token rows, kv_heads, head_dim]")
+    if gate_per_head or softcap or distance_bias is not None:
+        _require(not (keep_first and window), "decode_attention: capped or biased scores do not go with kept first keys")
+        _check(lib, lib.mir_decode_attention_scored_bf16(
+            qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
+            block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), rows, page_size, heads, kv_heads,
+            head_dim, scale, int(window or 0), partition, num_partitions, _ptr(scratch),
+            0 if scratch is None else scratch.numel(), _stream(), *gate_args, int(gate_per_head), float(softcap or 0.0),
+            _ptr(distance_bias), distance_bias.shape[0] if distance_bias is not None else 0))
+        return
     if keep_first and window:
         _cuda(numbering)
         _require(numbering is not None and numbering.dtype == torch.int32 and numbering.numel() >= rows,
@@ -1327,16 +1353,19 @@ def prefill_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tenso
                       page_size: int, heads: int, kv_heads: int, head_dim: int, scale: float,
                       window: Optional[int], tensor_cores: Optional[bool] = None,
                       portion_tokens: Optional[int] = None, keep_first: int = 0,
-                      sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
+                      sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                      gate_per_head: bool = False, softcap: Optional[float] = None,
+                      distance_bias: Optional[torch.Tensor] = None) -> None:
     """bf16 tensor-core attention for any mix of portions (row r owns tokens query_starts[r]..query_starts[r+1]
     of the packed qkv and out; the rows may be a part of the batch, `portion_tokens` then says how many tokens
     they have together).  `tensor_cores`: True runs the tcgen05 kernel, False the mma.sync kernel, None chooses.
     `keep_first`: with a window, the first keys of a request that every later query still sees.  `sinks`, `gate`: as
     paged_attention_generic takes them, in the kernels' epilogues (the gate's rows are those of the whole batch, as
-    out's are)."""
-    _cuda(qkv, out, k_pages, v_pages, block_table, query_starts, context_lens, sinks, gate)
+    out's are).  `gate_per_head`, `softcap`, `distance_bias`: as paged_attention_generic takes them; with any of them
+    the mma.sync kernel runs."""
+    _cuda(qkv, out, k_pages, v_pages, block_table, query_starts, context_lens, sinks, gate, distance_bias)
     tokens = out.shape[0]
-    _check_extras("prefill_attention", sinks, gate, out, heads)
+    _check_extras("prefill_attention", sinks, gate, out, heads, gate_per_head, distance_bias)
     gate_args = (_ptr(sinks), _ptr(gate), gate.stride(0) if gate is not None else 0)
     rows = context_lens.numel()
     _require(qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16
@@ -1347,6 +1376,15 @@ def prefill_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tenso
              and block_table.shape[0] >= rows, "prefill_attention: bad metadata")
     lib = library("bf16")
     keep_first = int(keep_first or 0) if window else 0
+    if gate_per_head or softcap or distance_bias is not None:
+        _require(not keep_first and not tensor_cores,
+                 "prefill_attention: capped or biased scores run the mma.sync kernel, without kept first keys")
+        _check(lib, lib.mir_prefill_attention_scored_bf16(
+            qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+            block_table.shape[1], query_starts.data_ptr(), context_lens.data_ptr(), rows, tokens, page_size, heads,
+            kv_heads, head_dim, scale, int(window or 0), _stream(), *gate_args, int(gate_per_head), float(softcap or 0.0),
+            _ptr(distance_bias), distance_bias.shape[0] if distance_bias is not None else 0))
+        return
     if tensor_cores is None:
         portion_tokens = tokens if portion_tokens is None else portion_tokens
         tensor_cores = (PREFILL_TENSOR_CORES and portion_tokens >= PREFILL_TENSOR_CORE_MIN_PORTION * rows

@@ -246,8 +246,28 @@ class SoftmaxAttention(Mixer):
         first = self.q_width + self.kv_columns
         gate = qkv[:, first:first + self.gate_width] if s.gate else None        # [tokens, heads * value_dim] or [tokens, heads]
         scored = s.softcap is not None or self.distance_bias is not None or s.gate_per_head
-        fast = self.env.dtype == torch.bfloat16 and s.head_dim in kernels.FAST_HEAD_DIMS and s.value_dim == s.head_dim \
-            and not scored
+        fast = self.env.dtype == torch.bfloat16 and s.head_dim in kernels.FAST_HEAD_DIMS and s.value_dim == s.head_dim
+        if fast and scored and not kept:
+            # capped or biased scores, or a gate per head: the mma.sync kernels know them (single tokens split over the
+            # keys, portions as tiles of queries)
+            extras = dict(sinks=self.sinks, gate_per_head=s.gate_per_head, softcap=s.softcap,
+                          distance_bias=self.distance_bias)
+            singles = ctx.num_rows if ctx.decode_only else ctx.single_rows
+            if singles:
+                longest = ctx.max_context if ctx.decode_only else ctx.single_context
+                partition, count, floats = kernels.decode_attention_kept_plan(singles, s.heads, s.head_dim, longest)
+                scratch = ctx.alloc((floats,), torch.float32) if floats else None
+                kernels.decode_attention(qkv[:singles], out[:singles], cache.k_pages, cache.v_pages,
+                                         group.block_table[:singles], ctx.positions, cache.page_size, s.heads,
+                                         s.kv_heads, s.head_dim, s.scale, s.window, partition, count, scratch,
+                                         gate=gate[:singles] if gate is not None else None, **extras)
+            if singles < ctx.num_rows:
+                kernels.prefill_attention(qkv, out, cache.k_pages, cache.v_pages, group.block_table[singles:],
+                                          ctx.query_starts[singles:], ctx.context_lens[singles:], cache.page_size,
+                                          s.heads, s.kv_heads, s.head_dim, s.scale, s.window, tensor_cores=False,
+                                          portion_tokens=out.shape[0] - singles, gate=gate, **extras)
+            return
+        fast = fast and not scored
         if fast and kept:
             # kept first keys: single tokens run the mma.sync kernel split over the keys, which walks the kept keys
             # and then the window's (the tcgen05 decode kernel does not know kept keys); portions run as tiles of

@@ -7,11 +7,40 @@ product of a position and a 32-bit frequency.
 
 from __future__ import annotations
 
+import json
 import math
+from pathlib import Path
 
+import numpy as np
 import torch
 
 F = torch.float64
+
+
+def read_model(folder):
+    """(config, {name: tensor}) of a folder with config.json and model.safetensors (an 8-byte length, a JSON table of
+    names, then the data)."""
+    folder = Path(folder)
+    config = json.loads((folder / "config.json").read_text())
+    raw = (folder / "model.safetensors").read_bytes()
+    size = int.from_bytes(raw[:8], "little")
+    table = json.loads(raw[8:8 + size])
+    body = raw[8 + size:]
+    weights = {}
+    for name, entry in table.items():
+        if name == "__metadata__":
+            continue
+        begin, end = entry["data_offsets"]
+        data = body[begin:end]
+        if entry["dtype"] == "BF16":
+            bits = np.frombuffer(data, dtype=np.uint16).astype(np.uint32) << 16
+            values = torch.from_numpy(bits.view(np.float32).copy())
+        elif entry["dtype"] == "F32":
+            values = torch.from_numpy(np.frombuffer(data, dtype=np.float32).copy())
+        else:
+            raise ValueError(f"{name}: dtype {entry['dtype']}")
+        weights[name] = values.reshape(entry["shape"]).to(F)
+    return config, weights
 
 
 def layer_norm(x, weight, bias, eps):
