@@ -166,7 +166,7 @@ def main() -> int:
                         help="decode / prefill: run only that phase, bracketed by cudaProfilerStart/Stop (for ncu "
                              "--profile-from-start off); the JSON line then holds only that phase")
     parser.add_argument("--no-graphs", action="store_true", help="decode steps as plain launches, not as CUDA graphs")
-    parser.add_argument("--design", default=None, choices=["doderax", "zufotar", "dalesun"],
+    parser.add_argument("--design", default=None, choices=["doderax", "zufotar", "dalesun", "gumazen"],
                         help="instead of the headline workload: prefill and decode throughput of this design at layer "
                              "sizes that resemble a real model's, beside the dense SwiGLU decoder of equal size, and its "
                              "kernels alone with their roofline fractions (bench_designs.py)")

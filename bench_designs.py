@@ -1,4 +1,4 @@
-"""`bench.py --design doderax | zufotar | dalesun`: prefill and decode throughput of a design at layer sizes that resemble a
+"""`bench.py --design doderax | zufotar | dalesun | gumazen`: prefill and decode throughput of a design at layer sizes that resemble a
 real model's (random weights), beside the dense SwiGLU decoder of equal width, depth and parameter count (and, for
 Zufotar, beside Doderax, the closest model of the framework: recurrent mixers and attention in parallel layers), and
 every kernel the design adds alone, with the fraction of its roofline, beside the like kernel of the closest model.
@@ -374,6 +374,156 @@ def dalesun_kernel_table(s, tools) -> dict:
     return table
 
 
+# Gumazen: a residual of four streams, layer norms, three kinds of attention in turn (rotated with remapped frequencies
+# and biases; capped scores with a bias by distance in a window and a gate per head; rotated, normed behind the rotation,
+# with a sink), the first feed-forward dense with a squared relu, the others routed experts of which some are identity
+# experts; the middle layers run twice.  `runs` is the number of layer runs of a step.
+GUMAZEN_SIZES = {
+    "w2048": dict(width=2048, streams=4, layers=8, loop=(2, 6, 2), runs=12, heads=16, kv_heads=4, dim=128, window=1024,
+                  softcap=30.0, bias_rows=32, bias_max=512.0, ff=8192, experts=56, identity=8, top=6, expert_ff=1024,
+                  groups=(8, 4), shared_ff=2048, vocab=65536),
+    "w4096": dict(width=4096, streams=4, layers=6, loop=(2, 4, 2), runs=8, heads=32, kv_heads=8, dim=128, window=2048,
+                  softcap=30.0, bias_rows=32, bias_max=1024.0, ff=14336, experts=56, identity=8, top=6, expert_ff=2048,
+                  groups=(8, 4), shared_ff=4096, vocab=65536),
+}
+
+
+def gumazen_config(s: dict) -> dict:
+    heads = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5}
+    scaled = {"type": "attention_3", "mixer": dict(heads, rot={"dims": s["dim"] // 2, "base": 500000.0, "scaling": {
+        "factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})}
+    biased = {"type": "attention_2", "mixer": dict(heads, softcap=s["softcap"], bias_max=s["bias_max"],
+                                                   bias_rows=s["bias_rows"], mask={"size": s["window"]})}
+    sink = {"type": "attention", "mixer": dict(heads, rot={"dims": s["dim"], "base": 10000.0})}
+    moe = {"kind": "moe", "expert": {"ff": s["expert_ff"]}, "shared": {"ff": s["shared_ff"]},
+           "router": {"experts": s["experts"], "identity": s["identity"], "top": s["top"], "scale": 2.5,
+                      "groups": {"count": s["groups"][0], "keep": s["groups"][1]}}}
+    kinds = (scaled, biased, sink)
+    layers = [dict(kinds[index % 3], mlp={"kind": "dense", "ff": s["ff"]} if index == 0 else moe)
+              for index in range(s["layers"])]
+    start, stop, times = s["loop"]
+    return {"architecture": "Gumazen", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5},
+            "streams": s["streams"], "loop": {"start": start, "stop": stop, "times": times}, "layers": layers}
+
+
+def gumazen_kernel_table(s, tools) -> dict:
+    """Every kernel the design adds or extends, alone, at the sizes of a 2,048-token prompt and of a step of 8 decoded
+    tokens: [microseconds, fraction of its roofline], beside the like kernel of the closest models (the dense decoder's
+    norm, q/k kernel and attention; Zufotar's router and the sum of its experts' rows)."""
+    import torch
+    from libmir_b200 import kernels
+    timed, copies, rand, device, hbm, flops_peak = (tools[k] for k in ("timed", "copies", "rand", "device", "hbm", "flops_peak"))
+    bf16, f32, i32 = torch.bfloat16, torch.float32, torch.int32
+    width, heads, kv_heads, dim, window, count = s["width"], s["heads"], s["kv_heads"], s["dim"], s["window"], s["streams"]
+    table = {}
+    for label, rows, portion in ((f"prefill_{PROMPT}", 1, PROMPT), (f"decode_b{BATCH}", BATCH, 1)):
+        tokens = rows * portion
+        prompt = portion > 1
+        starts = torch.arange(0, tokens + 1, portion, dtype=i32, device=device)
+        context = PROMPT if prompt else PROMPT + 1
+        positions = (torch.arange(tokens, dtype=i32, device=device) % portion) + (context - portion)
+        # ---- the residual's streams: the layer norm that reads their mix, the update that writes all of them
+        packs = copies(lambda: (rand(tokens, count, width, dtype=f32), rand(tokens, width, dtype=f32)), tokens * width * 4 * (count + 1))
+        w_a, w_b = rand(width, dtype=f32), rand(width, dtype=f32)
+        read, write = rand(count, dtype=f32), rand(count, dtype=f32)
+        mix = rand(count, count, dtype=f32)
+        out_w = torch.empty(tokens, width, device=device, dtype=bf16)
+        calls = [lambda p=p: kernels.layer_norm(p[0], w_a, w_b, 1e-5, out_w, None, read) for p in packs]
+        table[f"{label}_layer_norm_of_streams"] = timed(calls, tokens * width * (4 * count + 2), hbm)
+        calls = [lambda p=p: kernels.layer_norm(p[1], w_a, w_b, 1e-5, out_w) for p in packs]
+        table[f"{label}_layer_norm"] = timed(calls, tokens * width * 6, hbm)
+        calls = [lambda p=p: kernels.rms_norm(p[1], w_a, 1e-6, out_w) for p in packs]
+        table[f"{label}_dense_rms_norm"] = timed(calls, tokens * width * 6, hbm)
+        calls = [lambda p=p: kernels.streams_write(p[0], p[1], mix, write) for p in packs]
+        table[f"{label}_streams_write"] = timed(calls, tokens * width * 4 * (2 * count + 1), hbm)
+        if hasattr(kernels, "streams_write_norm"):
+            calls = [lambda p=p: kernels.streams_write_norm(p[0], p[1], mix, write, read, w_a, w_b, 1e-5, out_w) for p in packs]
+            table[f"{label}_streams_write_and_next_norm"] = timed(calls, tokens * width * (4 * (2 * count + 1) + 2), hbm)
+        # ---- q and k: the norm over a whole projection (with and without the rotation behind it), the rotation with the
+        # unweighted norm per head behind it; keys and values into pages; beside the dense decoder's kernel
+        pages_per_row = -(-(context + PAGE) // PAGE)
+        cache_rows = rows * pages_per_row * PAGE
+        banks = max(2, min(24, -(-(300 << 20) // (cache_rows * kv_heads * dim * 4))))
+        k_cache = [rand(cache_rows, kv_heads, dim, scale=0.5) for _ in range(banks)]
+        v_cache = [rand(cache_rows, kv_heads, dim, scale=0.5) for _ in range(banks)]
+        block_table = torch.arange(rows * pages_per_row, dtype=i32, device=device).view(rows, pages_per_row).contiguous()
+        contexts = torch.full((rows,), context, dtype=i32, device=device)
+        slot_map = (torch.arange(tokens, dtype=i32, device=device) // portion) * (pages_per_row * PAGE) + positions
+        packed_width = (heads + 2 * kv_heads) * dim
+        qkv = rand(tokens, packed_width + 8 * (-(-heads // 8)), scale=0.3)
+        plain_rows = rand(tokens, packed_width, scale=0.3)
+        q_whole, k_whole = torch.ones(heads * dim, device=device), torch.ones(kv_heads * dim, device=device)
+        norm_q, norm_k = torch.ones(dim, device=device), torch.ones(dim, device=device)
+        freq_half, freq_quarter = torch.rand(dim // 2, device=device, dtype=f32), torch.rand(dim // 4, device=device, dtype=f32)
+        moved = tokens * (heads + kv_heads) * dim * 4 + tokens * kv_heads * dim * 4
+        for name, args in (("qk_prepare_projection_norm_then_rotation", (freq_quarter, q_whole, k_whole, dim // 2, "projection", False)),
+                           ("qk_prepare_projection_norm", (None, q_whole, k_whole, 0, "projection", False)),
+                           ("qk_prepare_rotation_then_head_norm", (freq_half, None, None, dim, "head", True))):
+            freq, qw, kw, rotary, span, after = args
+            calls = [lambda k=k, v=v: kernels.qk_prepare(qkv, positions, slot_map, freq, qw, kw, k, v, heads, kv_heads, dim, dim,
+                                                         rotary, 1e-5, span, after_rotation=after) for k, v in zip(k_cache, v_cache)]
+            table[f"{label}_{name}"] = timed(calls, moved, hbm)
+        calls = [lambda k=k, v=v: kernels.qk_rope_store(plain_rows, positions, slot_map, freq_half, norm_q, norm_k, k, v, heads,
+                                                        kv_heads, dim, dim, 1e-6) for k, v in zip(k_cache, v_cache)]
+        table[f"{label}_dense_qk_rope_store"] = timed(calls, moved, hbm)
+        # ---- attention: capped scores with a bias by distance in a window and a gate per head; all keys with a sink;
+        # beside the dense decoder's in the same window and over all keys
+        gate = qkv[:, packed_width:packed_width + heads]
+        bias = rand(heads, min(window, int(s["bias_max"]) + 1), dtype=f32)
+        sinks = torch.zeros(heads, device=device, dtype=f32)
+        mixed = torch.empty(tokens, heads * dim, device=device, dtype=bf16)
+        scale = dim ** -0.5
+        scored = dict(gate=gate, gate_per_head=True, softcap=s["softcap"], distance_bias=bias)
+        if prompt:
+            in_window = 4.0 * sum(min(p + 1, window) for p in range(PROMPT)) * dim * heads
+            everything = 4.0 * (PROMPT * (PROMPT + 1) / 2) * dim * heads
+            for extras, span, flops, name in ((scored, window, in_window, "attention_window_capped_biased_gated"),
+                                              ({}, window, in_window, "dense_attention_window"),
+                                              ({"sinks": sinks}, None, everything, "attention_full_sink"),
+                                              ({}, None, everything, "dense_attention_full")):
+                calls = [lambda k=k, v=v, e=extras, w=span: kernels.prefill_attention(qkv, mixed, k, v, block_table, starts, contexts,
+                                                                                       PAGE, heads, kv_heads, dim, scale, w, **e)
+                         for k, v in zip(k_cache, v_cache)]
+                table[f"{label}_{name}"] = timed(calls, flops, flops_peak)
+        else:
+            q_positions = torch.full((tokens,), context - 1, dtype=i32, device=device)
+            for extras, span, name in ((scored, window, "attention_window_capped_biased_gated"), ({}, window, "dense_attention_window"),
+                                       ({"sinks": sinks}, None, "attention_full_sink"), ({}, None, "dense_attention_full")):
+                plan = kernels.decode_attention_scored_plan if (extras is scored and hasattr(kernels, "decode_attention_scored_plan")) \
+                    else (lambda r, h, kv, d, page, ctx: kernels.decode_attention_kept_plan(r, h, d, ctx)) if extras is scored \
+                    else kernels.decode_attention_plan
+                partition, parts, floats = plan(rows, heads, kv_heads, dim, PAGE, context)
+                scratch = torch.empty(max(floats, 1), device=device, dtype=f32)
+                key_bytes = rows * (min(span, context) if span else context) * kv_heads * dim * 2 * 2
+                calls = [lambda k=k, v=v, e=extras, w=span: kernels.decode_attention(qkv, mixed, k, v, block_table, q_positions, PAGE,
+                                                                                      heads, kv_heads, dim, scale, w, partition, parts,
+                                                                                      scratch if floats else None, **e)
+                         for k, v in zip(k_cache, v_cache)]
+                table[f"{label}_{name}"] = timed(calls, key_bytes, hbm)
+        # ---- the router (softmax scores, a group judged by its best, identity experts among the outputs) and the sum of
+        # the chosen experts' rows (identity experts add the input's row), beside Zufotar's
+        total, top = s["experts"] + s["identity"], s["top"]
+        logits = [rand(tokens, total + 8, dtype=f32) for _ in range(4)]
+        correction = rand(total, dtype=f32, scale=0.05)
+        ids = torch.empty(tokens, top, device=device, dtype=i32)
+        weights = torch.empty(tokens, top, device=device, dtype=f32)
+        route_bytes = tokens * (total * 4 + top * 8)
+        for kind, groups, name in (("softmax", "max", "moe_route_softmax_best_of_group"), ("sigmoid", "top2", "zufotar_moe_route")):
+            calls = [lambda l=l: kernels.moe_route(l, correction, False, ids, weights, None, total, top, s["groups"][0],
+                                                   s["groups"][1], 2.5, score=kind, group_score=groups) for l in logits]
+            table[f"{label}_{name}"] = timed(calls, route_bytes, hbm)
+        packs = copies(lambda: (rand(tokens * top, width, dtype=f32), rand(tokens, width, dtype=f32), rand(tokens, width, dtype=f32)),
+                       tokens * width * 4 * (top + 2))
+        x = rand(tokens, width)
+        combine_bytes = tokens * width * 4 * (top + 3)
+        calls = [lambda p=p: kernels.moe_combine(p[1], p[0], weights, p[2], None, overwrite=True, ids=ids,
+                                                 real_experts=s["experts"], identity_rows=x) for p in packs]
+        table[f"{label}_moe_combine_with_identity_experts"] = timed(calls, combine_bytes - tokens * width * 4, hbm)
+        calls = [lambda p=p: kernels.moe_combine(p[1], p[0], weights, p[2], None) for p in packs]
+        table[f"{label}_zufotar_moe_combine"] = timed(calls, combine_bytes, hbm)
+    return table
+
+
 def doderax_config(s: dict) -> dict:
     delta = {"heads": s["heads"], "kv_heads": s["heads"], "dim": s["dim"], "vdim": s["dim"], "conv": 4,
              "decay_rank": 64, "gate_rank": 64}
@@ -633,6 +783,21 @@ def run(args, peaks: dict) -> dict:
             entry["zufotar"] = model_numbers(zufotar_config(s), s["vocab"])
             entry["doderax"] = model_numbers(doderax_config(beside), s["vocab"])
             entry["dense_swiglu"] = model_numbers(dense_config(beside), s["vocab"])
+            report[name] = entry
+        return report
+    if args.design == "gumazen":
+        rand = lambda *shape, dtype=bf16, scale=1.0: (torch.randn(*shape, device=device, dtype=f32) * scale).to(dtype)
+        tools = {"timed": timed, "copies": copies, "rand": rand, "device": device, "hbm": hbm, "flops_peak": flops_peak}
+        report = {}
+        for name in [n for n in GUMAZEN_SIZES if args.design_sizes in ("all", n)]:
+            s = GUMAZEN_SIZES[name]
+            entry = {"sizes": s}
+            if not args.skip_points:
+                entry["kernels_us_and_fraction_of_roofline"] = gumazen_kernel_table(s, tools)
+                torch.cuda.empty_cache()
+            entry["gumazen"] = model_numbers(gumazen_config(s), s["vocab"])
+            entry["zufotar"] = model_numbers(zufotar_config(ZUFOTAR_SIZES[name]), s["vocab"])
+            entry["dense_swiglu"] = model_numbers(dense_config(dict(DESIGN_SIZES[name], layers=s["runs"])), s["vocab"])
             report[name] = entry
         return report
     if args.design == "dalesun":

@@ -20,8 +20,8 @@
 // has no key and no value and is not scaled.  gate (rows of the activations' type with a stride of their own, or
 // none): the head's result is multiplied by the sigmoid of its gate elements before it is stored; gate_per_head: a
 // gate row holds one number per head instead of one per element.
-// softcap > 0: score <- softcap * tanh(score / softcap) after the scale.  rel_bias ([rel_rows, heads] 32-bit, or none):
-// the row min(position - key, rel_rows - 1) of head h is added to the score after the cap (a bias by distance whose
+// softcap > 0: score <- softcap * tanh(score / softcap) after the scale.  rel_bias ([heads, rel_rows] 32-bit, or none):
+// the entry min(position - key, rel_rows - 1) of head h is added to the score after the cap (a bias by distance whose
 // buckets the host has spread out into one row per distance; from the last row on it no longer changes).
 #include <cfloat>
 #include "common.cuh"
@@ -90,7 +90,7 @@ __global__ void paged_attention_generic_kernel(
       }
       score = dot * scale;
       if (softcap > 0.0f) score = softcap * tanhf(score / softcap);
-      if (rel_bias != nullptr) score += rel_bias[(size_t)min(position - key, rel_rows - 1) * heads + head];
+      if (rel_bias != nullptr) score += rel_bias[(size_t)head * rel_rows + min(position - key, rel_rows - 1)];
     }
     const float next_max = fmaxf(running_max, warp_max(score));
     const float correction = expf(running_max - next_max);

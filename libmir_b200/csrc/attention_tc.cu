@@ -118,6 +118,12 @@ __device__ long long g_prompt_tiles[kTraceTiles * 16];
 #define ATT_STAMP(tile, index) do { } while (0)
 #endif
 
+// 1 / x to about one unit in the last place; 0 for inf.
+__device__ __forceinline__ float fast_reciprocal(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -158,11 +164,15 @@ struct Handoff {
   uint32_t to_barrier;
   float* to;
 };
-template <bool MASKED, bool SHARED>
+// SCORED: the scaled score is capped (softcap * tanh(score / softcap)) and gets the head's bias by distance (`bias`,
+// one entry per distance up to bias_last; `distance` is that of this thread's first column, the next column's is one
+// less), in 32-bit; from there on the scores are final and in units of log2 e.
+template <bool MASKED, bool SHARED, bool SCORED>
 __device__ __forceinline__ float softmax_tile(uint32_t scores, int first, int low, int high, float scale_log2,
                                               float& reference, float& factor, bool& grow,
                                               uint32_t (&packed)[kCols / 2], float* shared_max, int part, int team,
-                                              int stamp_tile, const Handoff& handoff, float& own_factor, bool& alive) {
+                                              int stamp_tile, const Handoff& handoff, float& own_factor, bool& alive,
+                                              float softcap, const float* __restrict__ bias, int bias_last, int distance) {
   float v[kCols];
 #pragma unroll
   for (int c0 = 0; c0 < kCols; c0 += 32) tmem_load_32_nowait(scores + first + c0, v + c0);
@@ -170,6 +180,37 @@ __device__ __forceinline__ float softmax_tile(uint32_t scores, int first, int lo
 #pragma unroll
   for (int c = 0; c < kCols; ++c) asm volatile("" : "+f"(v[c])::"memory");   // no use of v moves above the wait
   ATT_STAMP(stamp_tile, 7);
+  if (SCORED) {
+    // s' = cap * tanh(s / cap) + bias with tanh(y) = 1 - 2 / (1 + e^(2 y)) (exact at both ends, where e^(2 y) is 0 or
+    // inf; an absolute error of a few 1e-7 between), in units of log2 e:  s' log2 e = lift - 2 cap log2 e / (1 + 2^(v k))
+    // with k = 2 scale log2 e / cap and lift = (cap + bias) log2 e.  Without a cap: v scale log2 e + bias log2 e.
+    constexpr float kLog2e = 1.4426950408889634f;
+    const bool capped = softcap > 0.0f;
+    const float k = capped ? 2.0f * scale_log2 / softcap : scale_log2;
+    const float drop = -2.0f * softcap * kLog2e, base = capped ? softcap * kLog2e : 0.0f;
+    // the bias: most tiles lie wholly beyond the table's last entry (one value for all columns) or wholly inside it
+    const int nearest = distance - (kCols - 1);
+    if (bias == nullptr || nearest >= bias_last) {
+      const float lift = base + (bias != nullptr ? __ldg(bias + bias_last) * kLog2e : 0.0f);
+#pragma unroll
+      for (int c = 0; c < kCols; ++c)
+        v[c] = capped ? fmaf(drop, fast_reciprocal(1.0f + fast_exp2(v[c] * k)), lift) : fmaf(v[c], k, lift);
+    } else if (nearest >= 0 && distance <= bias_last) {
+      const float* entry = bias + distance;
+#pragma unroll
+      for (int c = 0; c < kCols; ++c) {
+        const float lift = fmaf(__ldg(entry - c), kLog2e, base);
+        v[c] = capped ? fmaf(drop, fast_reciprocal(1.0f + fast_exp2(v[c] * k)), lift) : fmaf(v[c], k, lift);
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < kCols; ++c) {
+        const float lift = fmaf(__ldg(bias + min(max(distance - c, 0), bias_last)), kLog2e, base);
+        v[c] = capped ? fmaf(drop, fast_reciprocal(1.0f + fast_exp2(v[c] * k)), lift) : fmaf(v[c], k, lift);
+      }
+    }
+    scale_log2 = 1.0f;
+  }
   if (MASKED) {
     // a hidden key's score becomes -inf by selection (whatever the cache held there, a NaN too), once; from here on
     // the tile is handled like any other: -inf never wins the maximum and its exponential is exactly 0
@@ -285,7 +326,7 @@ __device__ __forceinline__ int item_of(int k, int cta, int ctas, int items) {
   return k * ctas + ((k & 1) ? ctas - 1 - cta : cta);
 }
 
-template <int kStreams, bool kShared>
+template <int kStreams, bool kShared, bool kScored = false>
 __global__ void __launch_bounds__(threads_for(kStreams), 1)
 tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                             const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap k_tile_map,
@@ -580,12 +621,17 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         handoff.to_barrier = bar(REF_READY + (g & 1));
         handoff.to = &handed[g & 1][r];
         float own_factor;
-        const float sum = every ? softmax_tile<false, kShared>(scores, first, low, high, scale_log2, reference, factor, grow,
-                                                               packed, shared_max, part, team, stamp_tile, handoff,
-                                                               own_factor, alive)
-                                : softmax_tile<true, kShared>(scores, first, low, high, scale_log2, reference, factor, grow,
-                                                              packed, shared_max, part, team, stamp_tile, handoff,
-                                                              own_factor, alive);
+        const float* bias = (kScored && extras.rel_bias != nullptr)
+                                ? extras.rel_bias + (size_t)min(w.head, extras.rel_heads - 1) * extras.rel_rows : nullptr;
+        const int distance = position - key0 - first;         // of this thread's first column
+        const float sum = every ? softmax_tile<false, kShared, kScored>(scores, first, low, high, scale_log2, reference, factor,
+                                                                        grow, packed, shared_max, part, team, stamp_tile,
+                                                                        handoff, own_factor, alive, extras.softcap, bias,
+                                                                        extras.rel_rows - 1, distance)
+                                : softmax_tile<true, kShared, kScored>(scores, first, low, high, scale_log2, reference, factor,
+                                                                       grow, packed, shared_max, part, team, stamp_tile,
+                                                                       handoff, own_factor, alive, extras.softcap, bias,
+                                                                       extras.rel_rows - 1, distance);
         ATT_STAMP(stamp_tile, 9);
         denominator = denominator * own_factor + sum;
         // Split keys: this stream's previous product (tile t - kStreams) is over: S(t) was issued behind it, and the
@@ -678,7 +724,13 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             barrier_arrive(bar(O_FREE));
             ATT_STAMP(stamp_item, 3);
           }
-          if (valid_row && alive && extras.gate != nullptr) {
+          if (valid_row && alive && extras.gate != nullptr && extras.gate_head_width > 0) {
+            // one gate for the whole head of this token
+            const float g = __bfloat162float(extras.gate[(size_t)(w.q_row0 + r) * (size_t)extras.gate_stride + w.head]);
+            const float share = 1.0f / (1.0f + __expf(-g));
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] *= share;
+          } else if (valid_row && alive && extras.gate != nullptr) {
             // the gate's 32 elements of this token and head (16-byte pieces: the entry point checks the alignment)
             const bf16* gate = extras.gate + (size_t)(w.q_row0 + r) * (size_t)extras.gate_stride +
                                (size_t)w.head * kDim + column + c0;
@@ -748,19 +800,17 @@ MIR_EXPORT int mir_prefill_attention_tc_takes(int head_dim, int page_size) {
 // [cache_rows, kv_heads, 128].
 // keep_first: with a window, the first keys of every request that stay visible to all its later queries.
 // sinks, gate, gate_stride: what AttentionExtras describes (null for none); the gate's rows are read in 16-byte pieces.
-MIR_EXPORT int mir_prefill_attention_tc_extra_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
-                                                   const void* v_pages, long long cache_rows, const int* block_table,
-                                                   int table_width, const int* query_starts, const int* context_lens,
-                                                   int num_rows, int tokens, int page_size, int heads, int kv_heads,
-                                                   int head_dim, float scale, int window, int keep_first,
-                                                   cudaStream_t stream, const float* sinks, const void* gate,
-                                                   long long gate_stride) {
+static int prefill_attention_tc_with(const void* q, long long q_stride, void* out, const void* k_pages,
+                                     const void* v_pages, long long cache_rows, const int* block_table,
+                                     int table_width, const int* query_starts, const int* context_lens,
+                                     int num_rows, int tokens, int page_size, int heads, int kv_heads,
+                                     int head_dim, float scale, int window, int keep_first,
+                                     cudaStream_t stream, const AttentionExtras& extras) {
   if (num_rows == 0 || tokens == 0) return MIR_OK;
-  if (gate != nullptr && (((uintptr_t)gate & 15) || (gate_stride % 8))) {
+  if (extras.gate != nullptr && extras.gate_head_width == 0 && (((uintptr_t)extras.gate & 15) || (extras.gate_stride % 8))) {
     mir_set_error("prefill_attention_tc: the gate's rows must be 16-byte aligned");
     return MIR_BAD_ARGUMENT;
   }
-  const AttentionExtras extras{sinks, (const bf16*)gate, gate_stride};
   if (keep_first < 0) { mir_set_error("prefill_attention_tc: keep_first is negative"); return MIR_BAD_ARGUMENT; }
   if (!mir_prefill_attention_tc_takes(head_dim, page_size) || heads <= 0 || kv_heads <= 0 || heads % kv_heads ||
       table_width <= 0 || window < 0 || num_rows < 0 || tokens < 0 || scale <= 0.0f ||
@@ -793,6 +843,9 @@ MIR_EXPORT int mir_prefill_attention_tc_extra_bf16(const void* q, long long q_st
     if (err == cudaSuccess)
       err = cudaFuncSetAttribute(tc_prefill_attention_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  kSmemBytes);
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(tc_prefill_attention_kernel<2, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kSmemBytes);
     if (err != cudaSuccess) {
       mir_set_error("prefill_attention_tc: cannot reserve %d bytes of shared memory: %s", kSmemBytes,
                     cudaGetErrorString(err));
@@ -813,6 +866,11 @@ MIR_EXPORT int mir_prefill_attention_tc_extra_bf16(const void* q, long long q_st
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 148;
   }
   const int ctas = (int)std::min<long long>(items, g_ctas > 0 ? g_ctas : sms);
+  if (extras.softcap > 0.0f || extras.rel_bias != nullptr)   // capped or biased scores: two streams, a shared reference
+    return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel<2, true, true>, dim3(ctas), dim3(threads_for(2)),
+                      (size_t)kSmemBytes, stream, 0, q_map, k_map, v_map, k_tile_map, v_tile_map, (bf16*)out, block_table, table_width,
+                      query_starts, context_lens, num_rows, page_size, heads, kv_heads,
+                      scale * 1.4426950408889634f, window, tile_slots, window > 0 ? keep_first : 0, extras);
   if (g_streams == 2 && g_shared)
     return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel<2, true>, dim3(ctas), dim3(threads_for(2)),
                       (size_t)kSmemBytes, stream, 0, q_map, k_map, v_map, k_tile_map, v_tile_map, (bf16*)out, block_table, table_width,
@@ -827,6 +885,36 @@ MIR_EXPORT int mir_prefill_attention_tc_extra_bf16(const void* q, long long q_st
                     (size_t)kSmemBytes, stream, 0, q_map, k_map, v_map, k_tile_map, v_tile_map, (bf16*)out, block_table, table_width,
                     query_starts, context_lens, num_rows, page_size, heads, kv_heads,
                     scale * 1.4426950408889634f, window, tile_slots, window > 0 ? keep_first : 0, extras);
+}
+
+MIR_EXPORT int mir_prefill_attention_tc_extra_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                                   const void* v_pages, long long cache_rows, const int* block_table,
+                                                   int table_width, const int* query_starts, const int* context_lens,
+                                                   int num_rows, int tokens, int page_size, int heads, int kv_heads,
+                                                   int head_dim, float scale, int window, int keep_first,
+                                                   cudaStream_t stream, const float* sinks, const void* gate,
+                                                   long long gate_stride) {
+  const AttentionExtras extras{sinks, (const bf16*)gate, gate_stride};
+  return prefill_attention_tc_with(q, q_stride, out, k_pages, v_pages, cache_rows, block_table, table_width, query_starts,
+                                   context_lens, num_rows, tokens, page_size, heads, kv_heads, head_dim, scale, window,
+                                   keep_first, stream, extras);
+}
+
+// The same with scores that are capped (softcap > 0) and biased by distance (rel_bias [heads, rel_rows] 32-bit or
+// null), in 32-bit before the softmax, and with a gate of one column per head (gate_per_head).
+MIR_EXPORT int mir_prefill_attention_tc_scored_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                                    const void* v_pages, long long cache_rows, const int* block_table,
+                                                    int table_width, const int* query_starts, const int* context_lens,
+                                                    int num_rows, int tokens, int page_size, int heads, int kv_heads,
+                                                    int head_dim, float scale, int window, cudaStream_t stream,
+                                                    const float* sinks, const void* gate, long long gate_stride,
+                                                    int gate_per_head, float softcap, const float* rel_bias, int rel_rows) {
+  if (rel_bias != nullptr && rel_rows <= 0) { mir_set_error("prefill_attention_tc: a bias by distance needs entries"); return MIR_BAD_ARGUMENT; }
+  const AttentionExtras extras{sinks, (const bf16*)gate, gate_stride, gate_per_head ? head_dim : 0, softcap, rel_bias,
+                               rel_rows, heads};
+  return prefill_attention_tc_with(q, q_stride, out, k_pages, v_pages, cache_rows, block_table, table_width, query_starts,
+                                   context_lens, num_rows, tokens, page_size, heads, kv_heads, head_dim, scale, window, 0,
+                                   stream, extras);
 }
 
 MIR_EXPORT int mir_prefill_attention_tc_kept_bf16(const void* q, long long q_stride, void* out, const void* k_pages,

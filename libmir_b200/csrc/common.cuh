@@ -120,8 +120,9 @@ struct AttentionExtras {
   long long gate_stride = 0;
   // gate_head_width > 0: a gate row holds one number per head (of that many result columns) instead of one per column.
   int gate_head_width = 0;
-  // softcap > 0: score <- softcap * tanh(score / softcap) after the scale.  rel_bias [rel_rows, rel_heads] 32-bit (or
-  // null): the row min(query position - key position, rel_rows - 1) of the head is added after the cap.
+  // softcap > 0: score <- softcap * tanh(score / softcap) after the scale.  rel_bias [rel_heads, rel_rows] 32-bit (or
+  // null): the head's entry min(query position - key position, rel_rows - 1) is added after the cap (a head's entries
+  // lie side by side: neighbouring keys and queries read neighbouring words).
   float softcap = 0.0f;
   const float* rel_bias = nullptr;
   int rel_rows = 0, rel_heads = 0;
@@ -143,7 +144,7 @@ __device__ __forceinline__ float modified_score(const AttentionExtras& extras, f
   float x = score_log2 * 0.6931471805599453f;
   if (extras.softcap > 0.0f) x = extras.softcap * tanhf(x / extras.softcap);
   if (extras.rel_bias != nullptr)
-    x += extras.rel_bias[(size_t)min(max(distance, 0), extras.rel_rows - 1) * extras.rel_heads + min(head, extras.rel_heads - 1)];
+    x += extras.rel_bias[(size_t)min(head, extras.rel_heads - 1) * extras.rel_rows + min(max(distance, 0), extras.rel_rows - 1)];
   return x * 1.4426950408889634f;
 }
 

@@ -119,6 +119,10 @@ class StepContext(PartContext):
     # the block), and the one that the next block in the schedule starts with (set by the model); None if unknown.
     upcoming_norm: Optional[object] = None
     norm_after_block: Optional[object] = None
+    # a residual of several streams: who reads them first in the next block (norm, mixing tensors), and the normed
+    # rows that the update before left for that reader
+    streams_reader_after_block: Optional[tuple] = None
+    normed_streams: Optional[torch.Tensor] = None
 
     def alloc(self, shape, dtype: torch.dtype) -> torch.Tensor:
         return self.arena.alloc(shape, dtype)

@@ -40,6 +40,8 @@ _SIGNATURES = {
         "mir_layer_norm": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                            c_float, c_void_p],
         "mir_streams_write": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "mir_streams_write_norm": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_int, c_int, c_int, c_float, c_void_p],
         "mir_streams_spread": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "mir_streams_sum": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "mir_embed_pairs": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -109,6 +111,10 @@ _SIGNATURES = {
                                              c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p,
                                              c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_float,
                                              c_void_p, c_int],
+        "mir_prefill_attention_tc_scored_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
+                                                 c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                 c_float, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_float,
+                                                 c_void_p, c_int],
         "mir_prefill_attention_scored_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                               c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                               c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_float, c_void_p,
@@ -1028,6 +1034,28 @@ def streams_write(streams: torch.Tensor, branch: torch.Tensor, mix: torch.Tensor
                                       count, width, _stream()))
 
 
+def streams_write_norm(streams: torch.Tensor, branch: torch.Tensor, mix: torch.Tensor, write: torch.Tensor,
+                       read: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float,
+                       out: torch.Tensor) -> None:
+    """streams_write, and in the same pass over a token out = layer_norm(sum_s read[s] x_s) of the streams as the update
+    leaves them (what layer_norm with `read` would give for them): the next sublayer's input without a second trip of
+    the streams through memory."""
+    _cuda(streams, branch, mix, write, read, weight, bias, out)
+    tokens, count, width = streams.shape
+    _require(streams.dtype == torch.float32 and streams.is_contiguous() and branch.dtype == torch.float32
+             and branch.is_contiguous() and branch.shape == (tokens, width) and mix.dtype == torch.float32
+             and mix.is_contiguous() and mix.shape == (count, count) and write.dtype == torch.float32
+             and write.numel() == count and read.dtype == torch.float32 and read.numel() == count
+             and weight.dtype == torch.float32 and weight.numel() == width
+             and (bias is None or (bias.dtype == torch.float32 and bias.numel() == width)) and out.is_contiguous()
+             and out.shape == (tokens, width) and out.dtype in (torch.bfloat16, torch.float32),
+             "streams_write_norm: bad arguments")
+    lib = library("core")
+    _check(lib, lib.mir_streams_write_norm(_is_bf16(out), streams.data_ptr(), branch.data_ptr(), mix.data_ptr(),
+                                           write.data_ptr(), read.data_ptr(), weight.data_ptr(), _ptr(bias), out.data_ptr(),
+                                           tokens, count, width, eps, _stream()))
+
+
 def streams_spread(x: torch.Tensor, streams: torch.Tensor) -> None:
     """Every stream of streams [tokens, S, width] becomes a copy of x [tokens, width] (32-bit)."""
     _cuda(x, streams)
@@ -1216,7 +1244,7 @@ def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch
     latent that is read both ways) and v_pages is not looked at.  `sinks` (float32 [heads]): exp(sink_h) joins the
     denominator of head h's softmax.  `gate` ([tokens, heads * value_dim] view, unit column stride, out's dtype): the
     result is multiplied by its sigmoid; with `gate_per_head` it is [tokens, heads], one number per head.  `softcap`:
-    score <- softcap * tanh(score / softcap) after the scale.  `distance_bias` (float32 [rows, heads]): row
+    score <- softcap * tanh(score / softcap) after the scale.  `distance_bias` (float32 [heads, rows]): row
     min(query position - key position, rows - 1) is added to the scores after the cap."""
     if values_in_keys:
         v_pages = k_pages
@@ -1227,9 +1255,9 @@ def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch
                               and gate.shape == ((out.shape[0], heads) if gate_per_head else out.shape)),
              "paged_attention: the gate has out's dtype and out's shape, or one column per head")
     _require(distance_bias is None or (distance_bias.dtype == torch.float32 and distance_bias.is_contiguous()
-                                       and distance_bias.dim() == 2 and distance_bias.shape[1] == heads
-                                       and distance_bias.shape[0] > 0),
-             "paged_attention: the bias by distance is float32 [rows, heads]")
+                                       and distance_bias.dim() == 2 and distance_bias.shape[0] == heads
+                                       and distance_bias.shape[1] > 0),
+             "paged_attention: the bias by distance is float32 [heads, rows]")
     tokens = out.shape[0]
     value_dim = head_dim if value_dim is None else value_dim
     _require(out.is_contiguous() and out.shape[1] == heads * value_dim and qkv.dtype == out.dtype
@@ -1243,7 +1271,7 @@ def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch
         page_size, heads, kv_heads, head_dim, value_dim, scale, int(window or 0), int(keep_first or 0),
         head_dim if values_in_keys else 0, _ptr(sinks), _ptr(gate), gate.stride(0) if gate is not None else 0,
         int(gate_per_head), float(softcap or 0.0), _ptr(distance_bias),
-        distance_bias.shape[0] if distance_bias is not None else 0, _stream()))
+        distance_bias.shape[1] if distance_bias is not None else 0, _stream()))
 
 
 def _check_extras(what: str, sinks, gate, out: torch.Tensor, heads: int, gate_per_head: bool = False,
@@ -1254,9 +1282,9 @@ def _check_extras(what: str, sinks, gate, out: torch.Tensor, heads: int, gate_pe
                               and gate.shape == ((out.shape[0], heads) if gate_per_head else out.shape)),
              f"{what}: the gate has out's dtype and out's shape, or one column per head")
     _require(distance_bias is None or (distance_bias.dtype == torch.float32 and distance_bias.is_contiguous()
-                                       and distance_bias.dim() == 2 and distance_bias.shape[1] == heads
-                                       and distance_bias.shape[0] > 0),
-             f"{what}: the bias by distance is float32 [rows, heads]")
+                                       and distance_bias.dim() == 2 and distance_bias.shape[0] == heads
+                                       and distance_bias.shape[1] > 0),
+             f"{what}: the bias by distance is float32 [heads, rows]")
 
 
 FAST_HEAD_DIMS = (64, 128)      # what the tensor-core attention kernels take; other sizes use the reference kernel
@@ -1322,7 +1350,7 @@ def decode_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor
             block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), rows, page_size, heads, kv_heads,
             head_dim, scale, int(window or 0), partition, num_partitions, _ptr(scratch),
             0 if scratch is None else scratch.numel(), _stream(), *gate_args, int(gate_per_head), float(softcap or 0.0),
-            _ptr(distance_bias), distance_bias.shape[0] if distance_bias is not None else 0))
+            _ptr(distance_bias), distance_bias.shape[1] if distance_bias is not None else 0))
         return
     if keep_first and window:
         _cuda(numbering)
@@ -1361,8 +1389,8 @@ def prefill_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tenso
     they have together).  `tensor_cores`: True runs the tcgen05 kernel, False the mma.sync kernel, None chooses.
     `keep_first`: with a window, the first keys of a request that every later query still sees.  `sinks`, `gate`: as
     paged_attention_generic takes them, in the kernels' epilogues (the gate's rows are those of the whole batch, as
-    out's are).  `gate_per_head`, `softcap`, `distance_bias`: as paged_attention_generic takes them; with any of them
-    the mma.sync kernel runs."""
+    out's are).  `gate_per_head`, `softcap`, `distance_bias`: as paged_attention_generic takes them; both tile kernels
+    cap and bias the scores in 32-bit before the softmax."""
     _cuda(qkv, out, k_pages, v_pages, block_table, query_starts, context_lens, sinks, gate, distance_bias)
     tokens = out.shape[0]
     _check_extras("prefill_attention", sinks, gate, out, heads, gate_per_head, distance_bias)
@@ -1377,13 +1405,27 @@ def prefill_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tenso
     lib = library("bf16")
     keep_first = int(keep_first or 0) if window else 0
     if gate_per_head or softcap or distance_bias is not None:
-        _require(not keep_first and not tensor_cores,
-                 "prefill_attention: capped or biased scores run the mma.sync kernel, without kept first keys")
+        _require(not keep_first, "prefill_attention: capped or biased scores do not go with kept first keys")
+        scored_args = (*gate_args, int(gate_per_head), float(softcap or 0.0), _ptr(distance_bias),
+                       distance_bias.shape[1] if distance_bias is not None else 0)
+        if tensor_cores is None:
+            portion_tokens = tokens if portion_tokens is None else portion_tokens
+            tensor_cores = (PREFILL_TENSOR_CORES and portion_tokens >= PREFILL_TENSOR_CORE_MIN_PORTION * rows
+                            and bool(lib.mir_prefill_attention_tc_takes(head_dim, page_size))
+                            and k_pages.is_contiguous() and v_pages.is_contiguous() and scale > 0
+                            and (gate is None or gate_per_head or (gate.data_ptr() % 16 == 0 and gate.stride(0) % 8 == 0)))
+        if tensor_cores:
+            _require(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.shape == v_pages.shape,
+                     "prefill_attention: the tcgen05 kernel reads contiguous [rows, kv_heads, head_dim] pages")
+            _check(lib, lib.mir_prefill_attention_tc_scored_bf16(
+                qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0],
+                block_table.data_ptr(), block_table.shape[1], query_starts.data_ptr(), context_lens.data_ptr(), rows,
+                tokens, page_size, heads, kv_heads, head_dim, scale, int(window or 0), _stream(), *scored_args))
+            return
         _check(lib, lib.mir_prefill_attention_scored_bf16(
             qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
             block_table.shape[1], query_starts.data_ptr(), context_lens.data_ptr(), rows, tokens, page_size, heads,
-            kv_heads, head_dim, scale, int(window or 0), _stream(), *gate_args, int(gate_per_head), float(softcap or 0.0),
-            _ptr(distance_bias), distance_bias.shape[0] if distance_bias is not None else 0))
+            kv_heads, head_dim, scale, int(window or 0), _stream(), *scored_args))
         return
     if tensor_cores is None:
         portion_tokens = tokens if portion_tokens is None else portion_tokens

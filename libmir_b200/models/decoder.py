@@ -215,10 +215,15 @@ class DecoderModel:
         ctx.rounded_residual = None
         ctx.norm_after_block = None
         ctx.next_reads_residual = False
+        ctx.normed_streams = None
         for index, entry in enumerate(spec.schedule):
+            # who reads the streams first in the next block: this block's last update norms their mix on the way out
+            following = self.blocks[spec.schedule[index + 1].layer] if index + 1 < len(spec.schedule) else None
+            ctx.streams_reader_after_block = following.first_reader() if following is not None else None
             self.blocks[entry.layer].forward(ctx, ctx.cache_view(index), streams)
             if self.after_entry is not None:
                 self.after_entry(index, streams)
+        ctx.streams_reader_after_block = ctx.normed_streams = None
         kernels.streams_sum(streams, embedded)
         return embedded
 

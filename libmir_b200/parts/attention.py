@@ -146,9 +146,9 @@ class SoftmaxAttention(Mixer):
             self.distance_bias = self.bias_by_distance(tensors["rel_bias"].float())
 
     def bias_by_distance(self, table: torch.Tensor) -> torch.Tensor:
-        """The stored table [buckets, heads] spread out to one row per distance n = 0, 1, ...: row n is the table's
-        row bucket(n).  It ends where nothing changes any more (the last bucket is reached, or the window ends); the
-        kernels use its last row for every greater distance."""
+        """The stored table [buckets, heads] spread out to one entry per distance n = 0, 1, ... and laid out [heads,
+        distances] for the kernels: entry n is the table's row bucket(n).  It ends where nothing changes any more (the
+        last bucket is reached, or the window ends); the kernels use its last entry for every greater distance."""
         import math
         bias = self.spec.distance_bias
         rows, exact = bias.rows, bias.rows // 2
@@ -165,7 +165,7 @@ class SoftmaxAttention(Mixer):
             if buckets[-1] == rows - 1 or (self.spec.window is not None and n >= self.spec.window):
                 break
         index = torch.tensor(buckets, dtype=torch.long, device=table.device)
-        return table[index].contiguous()
+        return table[index].t().contiguous()
 
     def weight_bytes(self):
         return sum(t.numel() * t.element_size() for t in (self.w_qkv, self.w_o, self.b_qkv, self.b_o, self.sinks,
@@ -248,8 +248,8 @@ class SoftmaxAttention(Mixer):
         scored = s.softcap is not None or self.distance_bias is not None or s.gate_per_head
         fast = self.env.dtype == torch.bfloat16 and s.head_dim in kernels.FAST_HEAD_DIMS and s.value_dim == s.head_dim
         if fast and scored and not kept:
-            # capped or biased scores, or a gate per head: the mma.sync kernels know them (single tokens split over the
-            # keys, portions as tiles of queries)
+            # capped or biased scores, or a gate per head: single tokens run the mma.sync kernel split over the keys,
+            # portions run as tiles of queries on either tile kernel
             extras = dict(sinks=self.sinks, gate_per_head=s.gate_per_head, softcap=s.softcap,
                           distance_bias=self.distance_bias)
             singles = ctx.num_rows if ctx.decode_only else ctx.single_rows
@@ -264,7 +264,7 @@ class SoftmaxAttention(Mixer):
             if singles < ctx.num_rows:
                 kernels.prefill_attention(qkv, out, cache.k_pages, cache.v_pages, group.block_table[singles:],
                                           ctx.query_starts[singles:], ctx.context_lens[singles:], cache.page_size,
-                                          s.heads, s.kv_heads, s.head_dim, s.scale, s.window, tensor_cores=False,
+                                          s.heads, s.kv_heads, s.head_dim, s.scale, s.window,
                                           portion_tokens=out.shape[0] - singles, gate=gate, **extras)
             return
         fast = fast and not scored

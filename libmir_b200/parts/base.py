@@ -71,6 +71,10 @@ class PartContext:
     residual_stats = None
     next_reads_residual = False
     rounded_residual = None
+    # A residual of several streams: (norm, mixing tensors) of the sublayer that reads the streams first in the next
+    # block (set by the model, None at the end), and the normed rows the block before left for it.
+    streams_reader_after_block = None
+    normed_streams = None
 
     def take_rounded(self, residual: torch.Tensor) -> torch.Tensor:
         """The residual in the engine dtype: the copy the block before left, if it left one, else a cast."""

@@ -20,7 +20,8 @@ the norm and the residual sum are 32-bit.  m is LayerSpec.residual_scale.
 streams:  the residual is S copies x_1 .. x_S per token (hyper-connections).  For each of the two sublayers, with its
 stored mixing tensors in [S], mix [S, S] and out [S]:  u = sum_s in[s] x_s;  y = sublayer(norm(u));  then all streams
 at once from the old ones, x_t <- sum_s mix[s, t] x_s + out[t] y.  Everything outside the sublayer is 32-bit: the
-norm's kernel forms u on the way in, the sublayer leaves y in a 32-bit buffer, one kernel updates the streams.
+norm's kernel forms u on the way in, the sublayer leaves y in a 32-bit buffer, one kernel updates the streams and, in the
+same pass, forms and norms the mix that the next sublayer (of this block or the next) reads.
 """
 
 from __future__ import annotations
@@ -281,25 +282,40 @@ class StreamsBlock(Block):
     def cache_requirement(self):
         return self.mixer.cache_requirement()
 
+    def first_reader(self):
+        """(norm, mixing tensors) of the sublayer that reads the streams first."""
+        return self.mixer_norm, self.mixer_streams
+
     def forward(self, ctx, cache, residual):
-        from .. import kernels
         ctx.upcoming_norm = None             # the products' results go through the streams' update, not into a norm
         ctx.residual_stats = None
         tokens, _, width = residual.shape
         result = ctx.alloc((tokens, width), torch.float32)
-        x = self._read(ctx, self.mixer_norm, self.mixer_streams, residual)
+        x, ctx.normed_streams = ctx.normed_streams, None       # what the update before this block left, if it did
+        if x is None or x.shape[0] != tokens:
+            x = self.mixer_norm.forward(ctx, residual, read=self.mixer_streams.read)
+        after = ctx.streams_reader_after_block
         self.mixer.forward(ctx, cache, x, result, overwrite=True)
-        kernels.streams_write(residual, result, self.mixer_streams.mix, self.mixer_streams.write)
         if self.feed_forward is not None:
-            x = self._read(ctx, self.feed_forward_norm, self.feed_forward_streams, residual)
+            x = self._write(ctx, residual, result, self.mixer_streams, (self.feed_forward_norm, self.feed_forward_streams))
             self.feed_forward.forward(ctx, x, result, overwrite=True)
-            kernels.streams_write(residual, result, self.feed_forward_streams.mix, self.feed_forward_streams.write)
+            ctx.normed_streams = self._write(ctx, residual, result, self.feed_forward_streams, after)
+        else:
+            ctx.normed_streams = self._write(ctx, residual, result, self.mixer_streams, after)
         ctx.residual_stats = None
 
-    @staticmethod
-    def _read(ctx, norm, streams, residual):
-        """norm(sum_s in[s] x_s) in the engine dtype; the norm's kernel forms the mix on the way in."""
-        return norm.forward(ctx, residual, read=streams.read)
+    def _write(self, ctx, residual, result, streams, reader):
+        """The streams take a sublayer's result; with a reader (norm, mixing tensors) the same kernel leaves the normed
+        mix of the new streams that this reader starts from, which is returned."""
+        from .. import kernels
+        if reader is None:
+            kernels.streams_write(residual, result, streams.mix, streams.write)
+            return None
+        norm, following = reader
+        out = ctx.alloc((residual.shape[0], residual.shape[2]), self.env.dtype)
+        kernels.streams_write_norm(residual, result, streams.mix, streams.write, following.read, norm.weight, norm.bias,
+                                   norm.spec.eps, out)
+        return out
 
 
 ARRANGEMENTS = {"pre_norm": PreNormBlock, "parallel": ParallelBlock, "output_norm": OutputNormBlock,

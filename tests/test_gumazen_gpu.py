@@ -106,31 +106,64 @@ def test_streams_are_spread_updated_all_at_once_and_summed(count):
     close(total, streams.double().cpu().sum(1), 2e-6, "sum of the streams")
 
 
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+@pytest.mark.parametrize("count,width", [(1, 52), (2, 96), (3, 50), (4, 2304), (5, 64), (7, 33), (8, 128), (16, 40)])
+def test_the_update_of_the_streams_also_norms_the_next_readers_mix(dtype, tol, count, width):
+    """One kernel: the streams after a sublayer as streams_write leaves them, and the layer norm of the next reader's
+    mix of them; every count with a kernel of its own and the general one, widths with and without 16-byte rows."""
+    from libmir_b200 import kernels
+    generator = torch.Generator().manual_seed(count * 1000 + width)
+    tokens = 10
+    start = torch.randn(tokens, count, width, generator=generator) * 2.0 + 0.5
+    branch = torch.randn(tokens, width, generator=generator)
+    mix, write = torch.eye(count) + 0.4 * torch.randn(count, count, generator=generator), torch.randn(count, generator=generator)
+    read = torch.randn(count, generator=generator)
+    weight, bias = torch.randn(width, generator=generator), torch.randn(width, generator=generator)
+    streams = on_device(start)
+    out = torch.empty(tokens, width, dtype=dtype, device=device())
+    kernels.streams_write_norm(streams, on_device(branch), on_device(mix), on_device(write), on_device(read),
+                               on_device(weight), on_device(bias), 1e-5, out)
+    want = torch.einsum("st,xsw->xtw", mix.double(), start.double()) + write.double()[None, :, None] * branch.double()[:, None, :]
+    close(streams, want, 2e-6, "streams after a sublayer")
+    mixed = (read.double()[None, :, None] * want).sum(1)
+    close(out, plain.layer_norm(mixed, weight, bias, 1e-5), 8 * tol, "the next reader's normed mix")
+    twice = on_device(start)
+    kernels.streams_write(twice, on_device(branch), on_device(mix), on_device(write))
+    assert torch.equal(twice, streams), "the same streams as the update alone leaves"
+
+
 # ------------------------------------------------------------------------------ q/k treatment
 @pytest.mark.parametrize("dtype,tol", DTYPES)
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim,rotary,span,weighted,after", [
     (6, 2, 32, 16, 16, "projection", True, False), (4, 1, 64, 64, 24, "head", False, True),
     (3, 3, 20, 12, 0, "projection", True, False), (2, 1, 128, 128, 128, "head", False, True),
-    (1, 1, 16, 16, 16, "head", True, False), (2, 2, 8, 24, 8, None, False, False)])
-def test_queries_and_keys_are_normed_rotated_and_stored(dtype, tol, heads, kv_heads, dim, vdim, rotary, span, weighted, after):
+    (1, 1, 16, 16, 16, "head", True, False), (2, 2, 8, 24, 8, None, False, False),
+    (4, 1, 64, 64, 32, "projection", True, False), (4, 2, 64, 64, 0, "projection", True, False),
+    (3, 1, 128, 128, 48, "head", True, False), (5, 5, 32, 32, 16, "head", False, True),
+    (9, 3, 128, 128, 64, "projection", True, False), (2, 1, 256, 256, 256, "head", True, True)])
+@pytest.mark.parametrize("tokens", [13, 300])
+def test_queries_and_keys_are_normed_rotated_and_stored(dtype, tol, tokens, heads, kv_heads, dim, vdim, rotary, span, weighted, after):
     """The norm over a whole projection, per head without weights behind the rotation, per head with weights before
-    it, and none; rows with columns behind q, k and v that must stay as they are; a slot of -1 writes nothing."""
+    it, and none; rows with columns behind q, k and v that must stay as they are; a slot of -1 writes nothing.  Few
+    and many tokens; heads of 16-byte pieces in bfloat16 (the kernel with wide accesses: the whole head rotated, at
+    most half of it, none) and other sizes."""
     from libmir_b200 import kernels
     generator = torch.Generator().manual_seed(dim + heads)
-    tokens, extra, eps = 13, 8, 1e-5
+    extra, eps = 8, 1e-5
     q_width, k_width, v_width = heads * dim, kv_heads * dim, kv_heads * vdim
     packed = torch.randn(tokens, q_width + k_width + v_width + extra, generator=generator) * 2.0
     rows = on_device(packed, dtype)
     before = rows.clone()
-    positions = [40, 41, 42, 0, 1, 2, 3, 999, 7, 8, 9, 10, 11]
-    slots = [5, 6, 7, 20, 21, 22, 23, 2, -1, 30, 31, 32, 33]
+    positions = [40, 41, 42, 0, 1, 2, 3, 999, 7, 8, 9, 10, 11] + list(range(100, 87 + tokens))
+    slots = [5, 6, 7, 20, 21, 22, 23, 2, -1, 30, 31, 32, 33] + list(range(40, 27 + tokens))
+    pages = 40 + tokens
     rot = {"dims": rotary, "base": 700.0, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 32}}
     table = on_device(plain.frequencies(rot)) if rotary else None
     per = dim if span == "head" else None
     q_weight = 1.0 + 0.3 * torch.randn(per or q_width, generator=generator) if weighted else None
     k_weight = 1.0 + 0.3 * torch.randn(per or k_width, generator=generator) if weighted else None
-    k_pages = torch.full((40, kv_heads, dim), 77.0, dtype=dtype, device=device())
-    v_pages = torch.full((40, kv_heads, vdim), 77.0, dtype=dtype, device=device())
+    k_pages = torch.full((pages, kv_heads, dim), 77.0, dtype=dtype, device=device())
+    v_pages = torch.full((pages, kv_heads, vdim), 77.0, dtype=dtype, device=device())
     kernels.qk_prepare(rows, ints(positions), ints(slots), table, on_device(q_weight) if weighted else None,
                        on_device(k_weight) if weighted else None, k_pages, v_pages, heads, kv_heads, dim, vdim, rotary, eps,
                        span, after_rotation=after)
@@ -149,7 +182,7 @@ def test_queries_and_keys_are_normed_rotated_and_stored(dtype, tol, heads, kv_he
             u, v = x[..., :half], x[..., half:rotary]
             x = torch.cat([u * cos - v * sin, v * cos + u * sin, x[..., rotary:]], dim=-1)
         if span == "head" and after:
-            x = plain.unit_rms(x, eps)
+            x = plain.unit_rms(x, eps) * (weight.double() if weight is not None else 1.0)
         return x
     want_q = treated(source[:, :q_width], heads, q_weight).reshape(tokens, q_width)
     want_k = treated(source[:, q_width:q_width + k_width], kv_heads, k_weight)
@@ -159,20 +192,21 @@ def test_queries_and_keys_are_normed_rotated_and_stored(dtype, tol, heads, kv_he
     written = [t for t in range(tokens) if slots[t] >= 0]
     close(k_pages[[slots[t] for t in written]], want_k[written], tol, "keys in their pages")
     close(v_pages[[slots[t] for t in written]], want_v[written], tol, "values in their pages")
-    untouched = [s for s in range(40) if s not in slots]
+    untouched = [s for s in range(pages) if s not in slots]
     assert (k_pages[untouched] == 77.0).all() and (v_pages[untouched] == 77.0).all()
 
 
 # ------------------------------------------------------------------------------ attention
 def spread_bias(table, window, farthest):
-    """One row per distance from the bucket rule (the test's own restatement of what the part hands to the kernels)."""
+    """One entry per distance from the bucket rule, a head's entries side by side (the test's own restatement of what
+    the part hands to the kernels)."""
     rows, out, n = table.shape[0], [], 0
     while True:
         out.append(plain.distance_bucket(n, rows, farthest))
         n += 1
         if out[-1] == rows - 1 or (window is not None and n >= window):
             break
-    return table[out]
+    return table[out].t().contiguous()          # [heads, distances]
 
 
 def pool_of(keys, values, page, rng, dtype):
@@ -200,11 +234,13 @@ ATTENTION_CASES = [
     # dtype, heads, kv_heads, dim, vdim, page, window, softcap, bias rows and farthest, gate per head, sink, path
     (torch.float32, 4, 2, 24, 40, 8, 37, 6.0, (12, 50.0), True, False, "reference"),
     (torch.float32, 3, 1, 16, 16, 16, None, None, None, False, True, "reference"),
-    (BF16, 6, 3, 64, 64, 16, 96, 30.0, (32, 120.0), True, False, "reference"),
+    (BF16, 6, 2, 64, 64, 16, 90, 25.0, (28, 110.0), True, False, "reference"),
     (BF16, 4, 2, 64, 64, 4, 50, 8.0, (16, 70.0), True, False, "tiles"),
     (BF16, 2, 2, 128, 128, 16, 70, 20.0, (10, 64.0), True, False, "tiles"),
     (BF16, 8, 1, 64, 64, 8, 33, None, (6, 9.0), False, False, "tiles"),
     (BF16, 4, 4, 128, 128, 32, 200, 3.0, None, True, True, "tiles"),
+    (BF16, 4, 2, 128, 128, 16, 160, 12.0, (20, 300.0), True, False, "tiles"),
+    (BF16, 2, 1, 128, 128, 8, None, 40.0, (8, 400.0), False, False, "tiles"),
 ]
 
 
@@ -256,8 +292,9 @@ def test_attention_with_capped_biased_scores_where_keys_at_the_edges_stand_out(d
         q = torch.cat([qs[r][a:b].reshape(b - a, -1) for r, a, b in rows_of])
         gate = torch.cat([gates[r][a:b] for r, a, b in rows_of])
         filler = torch.zeros(q.shape[0], 8, dtype=F64)
-        rows = on_device(torch.cat([q, filler, gate], dim=1), dtype)
-        return rows, rows[:, q.shape[1] + 8:]
+        tail = torch.zeros(q.shape[0], -(q.shape[1] + 8 + gate.shape[1]) % 8, dtype=F64)      # rows of 16-byte pieces
+        rows = on_device(torch.cat([q, filler, gate, tail], dim=1), dtype)
+        return rows, rows[:, q.shape[1] + 8:q.shape[1] + 8 + gate.shape[1]]
     # portions that start in mid-request: the last tokens of every request
     portions = [(0, 150, 300), (1, 0, 19), (2, 64, 131)]
     rows, gate = packed(portions)
@@ -273,6 +310,13 @@ def test_attention_with_capped_biased_scores_where_keys_at_the_edges_stand_out(d
     else:
         kernels.prefill_attention(rows, out, k_pool, v_pool, table, starts, ints(lengths), page, heads, kv_heads, dim, scale,
                                   window, tensor_cores=False, gate=gate, **extras)
+        if dim == 128 and page % 8 == 0:                        # the tcgen05 kernel takes these sizes
+            close(out, want, tol, f"{path}: prompt portions, mma.sync")
+            out.zero_()
+            kernels.launch_counts(reset=True)
+            kernels.prefill_attention(rows, out, k_pool, v_pool, table, starts, ints(lengths), page, heads, kv_heads, dim,
+                                      scale, window, tensor_cores=True, gate=gate, **extras)
+            assert kernels.launch_counts().get("prefill_attention_tc", 0) == 1
     close(out, want, tol, f"{path}: prompt portions")
     if path == "reference":
         return
@@ -292,16 +336,16 @@ def test_attention_with_capped_biased_scores_where_keys_at_the_edges_stand_out(d
 
 
 def test_the_bias_table_is_spread_by_the_bucket_rule():
-    """What the attention part hands to the kernels: one row per distance, ending where the last bucket or the window's
+    """What the attention part hands to the kernels: one entry per distance and head [heads, distances], ending where the last bucket or the window's
     end is reached; for constants whose buckets fall on exact powers too."""
     from libmir_b200.config.spec import DistanceBiasSpec, SoftmaxAttentionSpec
     from libmir_b200.parts import BuildEnv, SoftmaxAttention
-    for rows, farthest, window in ((32, 120.0, 96), (12, 40.0, 20), (2, 5.0, 3), (8, 64.0, None), (5, 3.0, 200), (16, 70.0, 1)):
+    for rows, farthest, window in ((24, 150.0, 80), (12, 40.0, 20), (2, 5.0, 3), (8, 64.0, None), (5, 3.0, 200), (16, 70.0, 1)):
         spec = SoftmaxAttentionSpec(hidden_size=16, heads=3, kv_heads=1, head_dim=8, window=window,
                                     distance_bias=DistanceBiasSpec(rows=rows, farthest=farthest))
         part = SoftmaxAttention(spec, BuildEnv(torch.float32, torch.device("cpu")))
         table = torch.arange(rows * 3, dtype=torch.float32).view(rows, 3)
-        got = part.bias_by_distance(table)
+        got = part.bias_by_distance(table).t()
         for n in range(got.shape[0]):
             assert torch.equal(got[n], table[plain.distance_bucket(n, rows, farthest)])
         last = got.shape[0] - 1
@@ -555,7 +599,7 @@ def test_the_windows_edge_and_the_buckets_show_in_the_logits(tmp_path, dim, page
 
 def test_the_tensor_core_kernels_run_the_designs_attention_in_bfloat16(tmp_path):
     """Heads of 64 and 128 channels: prompts and single tokens of all three kinds of attention run the tile kernels
-    (capped and biased scores on mma.sync; the others where the sizes allow on tcgen05), not the reference kernel."""
+    (prompts of heads with 128 channels on tcgen05, the others on mma.sync), not the reference kernel."""
     from libmir_b200 import kernels
     for name in ("C", "D"):
         config = ALL[name]
@@ -566,7 +610,8 @@ def test_the_tensor_core_kernels_run_the_designs_attention_in_bfloat16(tmp_path)
         feed(model, "x", ids, [70, 1])
         counts = kernels.launch_counts()
         assert counts.get("paged_attention_generic", 0) == 0, counts
-        assert counts.get("prefill_attention", 0) > 0 and counts.get("decode_attention", 0) > 0, counts
+        tiles = "prefill_attention_tc" if name == "D" else "prefill_attention"      # heads of 128 channels: tcgen05
+        assert counts.get(tiles, 0) > 0 and counts.get("decode_attention", 0) > 0, counts
         assert counts.get("qk_prepare", 0) > 0 and counts.get("layer_norm", 0) > 0
 
 
