@@ -113,10 +113,10 @@ __global__ void qk_prepare_wide_kernel(__nv_bfloat16* __restrict__ qkv, long lon
                                        const float* __restrict__ inv_freq, const float* __restrict__ q_weight,
                                        const float* __restrict__ k_weight, __nv_bfloat16* __restrict__ k_pages,
                                        __nv_bfloat16* __restrict__ v_pages, int heads, int kv_heads, int rotary_dim,
-                                       float eps, int span, int after, int write_kv, int units_per_cta) {
+                                       float eps, int span, int after, int write_kv, int units_per_cta, int resident) {
   constexpr int HALF = 8 * L, DIM = 2 * HALF, GROUPS = 32 / L;
   __shared__ float angles[DIM];                      // [pairs] cosines then [pairs] sines of this token
-  __shared__ float scratch[32];
+  __shared__ float scratch[64];
   grid_launch_dependents();
   const int token = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
@@ -130,7 +130,7 @@ __global__ void qk_prepare_wide_kernel(__nv_bfloat16* __restrict__ qkv, long lon
     sincosf(position * inv_freq[pair], &angles[pairs + pair], &angles[pair]);
   grid_dependency_wait();
   float inverse_q = 1.0f, inverse_k = 1.0f;
-  if (span == 2) {
+  if (span == 2 && !resident) {
     const int q_pieces = heads * DIM / 8, k_pieces = kv_heads * DIM / 8;
     float sum_q = 0.0f, sum_k = 0.0f;
     for (int piece = threadIdx.x; piece < q_pieces + k_pieces; piece += blockDim.x) {
@@ -147,16 +147,17 @@ __global__ void qk_prepare_wide_kernel(__nv_bfloat16* __restrict__ qkv, long lon
     // both sums through one barrier: a warp's two sums side by side, then every thread adds the warps' in order
     sum_q = warp_sum(sum_q);
     sum_k = warp_sum(sum_k);
-    if (lane == 0) { scratch[warp] = sum_q; scratch[16 + warp] = sum_k; }
+    if (lane == 0) { scratch[warp] = sum_q; scratch[32 + warp] = sum_k; }
     __syncthreads();
     sum_q = sum_k = 0.0f;
-    for (int w = 0; w < warps; ++w) { sum_q += scratch[w]; sum_k += scratch[16 + w]; }
+    for (int w = 0; w < warps; ++w) { sum_q += scratch[w]; sum_k += scratch[32 + w]; }
     inverse_q = rsqrtf(sum_q / (float)(heads * DIM) + eps);
     inverse_k = rsqrtf(sum_k / (float)(kv_heads * DIM) + eps);
   }
   __syncthreads();
   const int unit_begin = blockIdx.y * units_per_cta, unit_end = min(units, unit_begin + units_per_cta);
-  for (int base = unit_begin + warp * GROUPS; base < unit_end; base += warps * GROUPS) {
+  // (resident: the CTA's warps hold all the token's heads at once, every warp runs the loop's body exactly once)
+  for (int base = unit_begin + warp * GROUPS; resident || base < unit_end; base += warps * GROUPS) {
     const int unit = base + group;
     const bool active = unit < unit_end;
     const bool is_query = unit < heads, is_value = unit >= heads + kv_heads;
@@ -184,6 +185,20 @@ __global__ void qk_prepare_wide_kernel(__nv_bfloat16* __restrict__ qkv, long lon
     }
     const bool treated = active && !is_value;
     const int local = is_query ? unit : unit - heads;
+    if (span == 2 && resident) {
+      // the norm over a projection from the pieces in registers: nothing is read twice, and nothing is written
+      // before every warp has its pieces
+      float sum = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sum = fmaf(fa[i], fa[i], fmaf(fb[i], fb[i], sum));
+      const float sum_q = warp_sum(treated && is_query ? sum : 0.0f), sum_k = warp_sum(treated && !is_query ? sum : 0.0f);
+      if (lane == 0) { scratch[warp] = sum_q; scratch[32 + warp] = sum_k; }
+      __syncthreads();
+      float total_q = 0.0f, total_k = 0.0f;
+      for (int w = 0; w < warps; ++w) { total_q += scratch[w]; total_k += scratch[32 + w]; }
+      inverse_q = rsqrtf(total_q / (float)(heads * DIM) + eps);
+      inverse_k = rsqrtf(total_k / (float)(kv_heads * DIM) + eps);
+    }
     const float* weight = !treated ? nullptr : (is_query ? q_weight : k_weight);
     if (span == 2 || (span == 1 && !after)) {          // the norm before the rotation
       float inverse = is_query ? inverse_q : inverse_k;
@@ -242,7 +257,7 @@ __global__ void qk_prepare_wide_kernel(__nv_bfloat16* __restrict__ qkv, long lon
         }
       }
     }
-    if (!writes) continue;
+    if (writes) {
     if (!is_value) {
       __nv_bfloat162* ha = reinterpret_cast<__nv_bfloat162*>(&a);
       __nv_bfloat162* hb = reinterpret_cast<__nv_bfloat162*>(&b);
@@ -254,8 +269,14 @@ __global__ void qk_prepare_wide_kernel(__nv_bfloat16* __restrict__ qkv, long lon
     }
     *reinterpret_cast<uint4*>(dst + 8 * l) = a;                // a value head is copied as it is
     *reinterpret_cast<uint4*>(dst + HALF + 8 * l) = b;
+    }
+    if (resident) break;
   }
 }
+
+// The most warps of a CTA that holds a token's heads in registers for the norm over a projection; wider tokens are
+// summed in a pass of their own by CTAs of eight warps (more of which fit an SM).
+int g_resident_warps = 16;
 
 template <int L>
 int launch_prepare_wide(__nv_bfloat16* qkv, long long row_stride, const int* positions, const int* slot_mapping,
@@ -266,15 +287,27 @@ int launch_prepare_wide(__nv_bfloat16* qkv, long long row_stride, const int* pos
   // one CTA of 8 warps per token, or with few tokens CTAs of 4 warps that share a token's heads; the norm over a
   // projection sums the whole row before any of its heads is overwritten in place, so there a token stays in one CTA
   const bool many = tokens >= 256 || span == 2;
-  const int threads = many ? 256 : 128;
+  int threads = many ? 256 : 128;
   const int units_per_cta = many ? units : 4 * (32 / L);
+  // the norm over a projection: if the token's heads fit a CTA's warps at once, the pieces stay in registers between
+  // the sum and the treatment
+  const int warps_for_all = (units + 32 / L - 1) / (32 / L);
+  const int resident = span == 2 && warps_for_all <= g_resident_warps;
+  if (resident) threads = 32 * warps_for_all;
   const dim3 grid(tokens, (units + units_per_cta - 1) / units_per_cta);
   return mir_launch_with(mir_pdl_for_streaming(), "qk_prepare", qk_prepare_wide_kernel<L>, grid, dim3(threads), 0, stream, 0,
                          qkv, row_stride, positions, slot_mapping, inv_freq, q_weight, k_weight, k_pages, v_pages, heads,
-                         kv_heads, rotary_dim, eps, span, after, write_kv, units_per_cta);
+                         kv_heads, rotary_dim, eps, span, after, write_kv, units_per_cta, resident);
 }
 
 }  // namespace
+
+// For measurements: the limit described at g_resident_warps (0: always the pass of its own).
+MIR_EXPORT int mir_qk_prepare_set_resident_warps(int warps) {
+  if (warps < 0 || warps > 32) { mir_set_error("qk_prepare: 0 to 32 warps"); return MIR_BAD_ARGUMENT; }
+  g_resident_warps = warps;
+  return MIR_OK;
+}
 
 // qkv: packed rows with row_stride elements from one token to the next (at least the width of q, k and v; what lies
 // behind them is left alone).  inv_freq [rotary_dim / 2] (null with rotary_dim 0).  q_weight, k_weight: 32-bit, null

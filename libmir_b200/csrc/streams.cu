@@ -39,11 +39,25 @@ __device__ __forceinline__ void store_columns(T* dst, const float (&values)[V]) 
   }
 }
 
+// A block's sum through one barrier: the warps' sums side by side in `slots` (32 floats that nothing else uses), then
+// every thread adds them in the warps' order.  The result depends on the values and on blockDim alone.
+__device__ __forceinline__ float block_sum_once(float v, float* slots) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  if (lane == 0) slots[warp] = v;
+  __syncthreads();
+  float total = 0.0f;
+  for (int w = 0; w < warps; ++w) total += slots[w];
+  return total;
+}
+
 // The second and third pass of a layer norm over the row in shared memory (its sum is known): mean, variance, result.
+// A thread reads back only the columns it wrote itself, so the two sums' barriers are the only ones (`scratch`: 64
+// floats, one half per sum).
 template <typename T, int V>
 __device__ __forceinline__ void norm_row(const float* row_values, float sum, float* scratch, const float* __restrict__ weight,
                                          const float* __restrict__ bias, T* __restrict__ dst, int width, float eps) {
-  const float mean = block_sum(sum, scratch) / (float)width;
+  const float mean = block_sum_once(sum, scratch) / (float)width;
   float squares = 0.0f;
   for (int c = threadIdx.x * V; c < width; c += blockDim.x * V) {
 #pragma unroll
@@ -52,24 +66,29 @@ __device__ __forceinline__ void norm_row(const float* row_values, float sum, flo
       squares = fmaf(d, d, squares);
     }
   }
-  const float inverse = rsqrtf(block_sum(squares, scratch) / (float)width + eps);
+  const float inverse = rsqrtf(block_sum_once(squares, scratch + 32) / (float)width + eps);
   for (int c = threadIdx.x * V; c < width; c += blockDim.x * V) {
     float values[V];
-#pragma unroll
-    for (int v = 0; v < V; ++v) {
-      values[v] = (row_values[c + v] - mean) * inverse * weight[c + v];
-      if (bias != nullptr) values[v] += bias[c + v];
+    alignas(16) float w[V], b[V];
+    if constexpr (V == 4) {
+      *reinterpret_cast<float4*>(w) = __ldg(reinterpret_cast<const float4*>(weight + c));
+      *reinterpret_cast<float4*>(b) = bias != nullptr ? __ldg(reinterpret_cast<const float4*>(bias + c)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    } else {
+      w[0] = weight[c];
+      b[0] = bias != nullptr ? bias[c] : 0.0f;
     }
+#pragma unroll
+    for (int v = 0; v < V; ++v) values[v] = fmaf((row_values[c + v] - mean) * inverse, w[v], b[v]);
     store_columns<T, V>(dst + c, values);
   }
 }
 
 template <typename T, int V>
-__global__ void layer_norm_kernel(const float* __restrict__ x, int streams, const float* __restrict__ read,
+__global__ void __launch_bounds__(512, 3) layer_norm_kernel(const float* __restrict__ x, int streams, const float* __restrict__ read,
                                   const float* __restrict__ weight, const float* __restrict__ bias, T* __restrict__ out,
                                   const int* __restrict__ rows, int width, float eps) {
   extern __shared__ float row_values[];            // [width]
-  __shared__ float scratch[32];
+  __shared__ float scratch[64];
   grid_launch_dependents();
   grid_dependency_wait();
   const int token = rows != nullptr ? rows[blockIdx.x] : blockIdx.x;
@@ -160,7 +179,7 @@ __global__ void streams_write_norm_kernel(float* __restrict__ x, const float* __
                                           const float* __restrict__ bias, T* __restrict__ out, int streams_given,
                                           int width, float eps) {
   extern __shared__ float row_values[];            // [width]
-  __shared__ float scratch[32];
+  __shared__ float scratch[64];
   __shared__ float m[kMaxStreams * kMaxStreams + 2 * kMaxStreams];
   constexpr int kCount = S > 0 ? S : kMaxStreams;
   const int streams = S > 0 ? S : streams_given;

@@ -1231,6 +1231,15 @@ def qk_prepare(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Optiona
                                    int(after_rotation), int(write_kv), _stream()))
 
 
+def set_qk_prepare_resident_warps(warps: int) -> None:
+    """For measurements: up to how many warps a CTA of qk_prepare may have to hold all heads of a token in registers
+    for the norm over a projection (0: the row is always summed in a pass of its own)."""
+    lib = library("core")
+    lib.mir_qk_prepare_set_resident_warps.argtypes = [c_int]
+    lib.mir_qk_prepare_set_resident_warps.restype = c_int
+    _check(lib, lib.mir_qk_prepare_set_resident_warps(int(warps)))
+
+
 def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                             block_table: torch.Tensor, row_of_token: torch.Tensor, positions: torch.Tensor,
                             page_size: int, heads: int, kv_heads: int, head_dim: int, scale: float,
