@@ -380,23 +380,23 @@ def dalesun_kernel_table(s, tools) -> dict:
 # experts; the middle layers run twice.  `runs` is the number of layer runs of a step.
 GUMAZEN_SIZES = {
     "w2048": dict(width=2048, streams=4, layers=8, loop=(2, 6, 2), runs=12, heads=16, kv_heads=4, dim=128, window=1024,
-                  softcap=30.0, bias_rows=32, bias_max=512.0, ff=8192, experts=56, identity=8, top=6, expert_ff=1024,
+                  softcap=50.0, bias_rows=32, bias_max=512.0, ff=8192, experts=56, identity=8, top=6, expert_ff=1024,
                   groups=(8, 4), shared_ff=2048, vocab=65536),
     "w4096": dict(width=4096, streams=4, layers=6, loop=(2, 4, 2), runs=8, heads=32, kv_heads=8, dim=128, window=2048,
-                  softcap=30.0, bias_rows=32, bias_max=1024.0, ff=14336, experts=56, identity=8, top=6, expert_ff=2048,
+                  softcap=50.0, bias_rows=32, bias_max=1024.0, ff=14336, experts=56, identity=8, top=6, expert_ff=2048,
                   groups=(8, 4), shared_ff=4096, vocab=65536),
 }
 
 
 def gumazen_config(s: dict) -> dict:
     heads = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5}
-    scaled = {"type": "attention_3", "mixer": dict(heads, rot={"dims": s["dim"] // 2, "base": 500000.0, "scaling": {
-        "factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})}
+    scaled = {"type": "attention_3", "mixer": dict(heads, rot={"dims": s["dim"] // 2, "base": 1000000.0, "scaling": {
+        "factor": 4.0, "low": 1.0, "high": 4.0, "original": 4096}})}
     biased = {"type": "attention_2", "mixer": dict(heads, softcap=s["softcap"], bias_max=s["bias_max"],
                                                    bias_rows=s["bias_rows"], mask={"size": s["window"]})}
     sink = {"type": "attention", "mixer": dict(heads, rot={"dims": s["dim"], "base": 10000.0})}
     moe = {"kind": "moe", "expert": {"ff": s["expert_ff"]}, "shared": {"ff": s["shared_ff"]},
-           "router": {"experts": s["experts"], "identity": s["identity"], "top": s["top"], "scale": 2.5,
+           "router": {"experts": s["experts"], "identity": s["identity"], "top": s["top"], "scale": 2.0,
                       "groups": {"count": s["groups"][0], "keep": s["groups"][1]}}}
     kinds = (scaled, biased, sink)
     layers = [dict(kinds[index % 3], mlp={"kind": "dense", "ff": s["ff"]} if index == 0 else moe)
