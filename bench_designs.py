@@ -489,9 +489,7 @@ def gumazen_kernel_table(s, tools) -> dict:
             q_positions = torch.full((tokens,), context - 1, dtype=i32, device=device)
             for extras, span, name in ((scored, window, "attention_window_capped_biased_gated"), ({}, window, "dense_attention_window"),
                                        ({"sinks": sinks}, None, "attention_full_sink"), ({}, None, "dense_attention_full")):
-                plan = kernels.decode_attention_scored_plan if (extras is scored and hasattr(kernels, "decode_attention_scored_plan")) \
-                    else (lambda r, h, kv, d, page, ctx: kernels.decode_attention_kept_plan(r, h, d, ctx)) if extras is scored \
-                    else kernels.decode_attention_plan
+                plan = kernels.decode_attention_plan
                 partition, parts, floats = plan(rows, heads, kv_heads, dim, PAGE, context)
                 scratch = torch.empty(max(floats, 1), device=device, dtype=f32)
                 key_bytes = rows * (min(span, context) if span else context) * kv_heads * dim * 2 * 2

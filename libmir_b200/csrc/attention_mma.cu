@@ -901,11 +901,12 @@ MIR_EXPORT long long mir_decode_attention_scratch_floats(int rows, int heads, in
 
 // The merge of the partitions' results alone (the tcgen05 decode kernel leaves them in the same layout): scratch as
 // mir_decode_attention_bf16 lays it out, partial outputs then (maximum, denominator) pairs.
-MIR_EXPORT int mir_decode_merge_extra_bf16(const float* partial_o, const float* partial_ml, const int* positions,
+// gate_head_width > 0: the gate's rows hold one number per head (of that many result columns).
+MIR_EXPORT int mir_decode_merge_gated_bf16(const float* partial_o, const float* partial_ml, const int* positions,
                                            int rows, int heads, int head_dim, int window, int partition,
                                            int num_partitions, void* out, cudaStream_t stream, const float* sinks,
-                                           const void* gate, long long gate_stride) {
-  const AttentionExtras extras{sinks, (const bf16*)gate, gate_stride};
+                                           const void* gate, long long gate_stride, int gate_head_width) {
+  const AttentionExtras extras{sinks, (const bf16*)gate, gate_stride, gate_head_width};
   if (rows <= 0 || rows > 65535 || heads <= 0 || partition <= 0 || num_partitions <= 0 || window < 0 ||
       (head_dim != 64 && head_dim != 128) || partial_o == nullptr || partial_ml == nullptr) {
     mir_set_error("decode_merge: bad sizes (rows %d, heads %d, head_dim %d, partition %d, partitions %d)", rows, heads,
@@ -917,6 +918,14 @@ MIR_EXPORT int mir_decode_merge_extra_bf16(const float* partial_o, const float* 
                             stream, extras);
   return launch_merge<128>(partial_o, partial_ml, positions, rows, heads, window, partition, num_partitions, (bf16*)out,
                            stream, extras);
+}
+
+MIR_EXPORT int mir_decode_merge_extra_bf16(const float* partial_o, const float* partial_ml, const int* positions,
+                                           int rows, int heads, int head_dim, int window, int partition,
+                                           int num_partitions, void* out, cudaStream_t stream, const float* sinks,
+                                           const void* gate, long long gate_stride) {
+  return mir_decode_merge_gated_bf16(partial_o, partial_ml, positions, rows, heads, head_dim, window, partition,
+                                     num_partitions, out, stream, sinks, gate, gate_stride, 0);
 }
 
 MIR_EXPORT int mir_decode_merge_bf16(const float* partial_o, const float* partial_ml, const int* positions, int rows,

@@ -322,9 +322,12 @@ tc_decode_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __gr
       float s[G];
       tmem_load<G>(tmem_s + lane_bits, s);
       float* mine = &exchange[t & 1][warp][0];
+      const bool modified = scores_modified(extras);      // a cap and a bias by distance, in 32-bit
 #pragma unroll
       for (int g = 0; g < G; ++g) {
-        s[g] = visible ? s[g] * scale_log2 : -INFINITY;
+        float value = s[g] * scale_log2;
+        if (modified && visible) value = modified_score(extras, value, position - key, head0 + g);
+        s[g] = visible ? value : -INFINITY;
         const float top = warp_max(s[g]);
         if (lane == g) mine[g] = top;
       }
@@ -452,15 +455,13 @@ MIR_EXPORT int mir_decode_attention_tc_takes(int head_dim, int page_size, int pa
 
 // One token per row, as mir_decode_attention_bf16; k_pages and v_pages are [cache_rows, kv_heads, 128].  sinks, gate,
 // gate_stride: what AttentionExtras describes (null for none).
-MIR_EXPORT int mir_decode_attention_tc_extra_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
-                                                  const void* v_pages, long long cache_rows, const int* block_table,
-                                                  int table_width, const int* positions, int rows, int page_size,
-                                                  int heads, int kv_heads, int head_dim, float scale, int window,
-                                                  int partition, int num_partitions, float* scratch,
-                                                  long long scratch_floats, cudaStream_t stream, const float* sinks,
-                                                  const void* gate, long long gate_stride) {
+static int decode_attention_tc_with(const void* q, long long q_stride, void* out, const void* k_pages,
+                                    const void* v_pages, long long cache_rows, const int* block_table,
+                                    int table_width, const int* positions, int rows, int page_size,
+                                    int heads, int kv_heads, int head_dim, float scale, int window,
+                                    int partition, int num_partitions, float* scratch,
+                                    long long scratch_floats, cudaStream_t stream, const AttentionExtras& extras) {
   if (rows == 0) return MIR_OK;
-  const AttentionExtras extras{sinks, (const bf16*)gate, gate_stride};
   if (!mir_decode_attention_tc_takes(head_dim, page_size, partition) || heads <= 0 || kv_heads <= 0 ||
       heads % kv_heads || table_width <= 0 || window < 0 || rows < 0 || rows > 65535 || num_partitions <= 0 ||
       num_partitions > 65535 || (q_stride % 8) || q_stride < (long long)heads * kDim || ((uintptr_t)q & 15) ||
@@ -496,8 +497,40 @@ MIR_EXPORT int mir_decode_attention_tc_extra_bf16(const void* q, long long q_str
   status = columns <= 4 ? MIR_SPLIT(4) : (columns <= 8 ? MIR_SPLIT(8) : MIR_SPLIT(16));
 #undef MIR_SPLIT
   if (status != MIR_OK || num_partitions == 1) return status;
-  return mir_decode_merge_extra_bf16(partial_o, partial_ml, positions, rows, heads, head_dim, window, partition,
-                                     num_partitions, out, stream, sinks, gate, gate_stride);
+  return mir_decode_merge_gated_bf16(partial_o, partial_ml, positions, rows, heads, head_dim, window, partition,
+                                     num_partitions, out, stream, extras.sinks, extras.gate, extras.gate_stride,
+                                     extras.gate_head_width);
+}
+
+MIR_EXPORT int mir_decode_attention_tc_extra_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                                  const void* v_pages, long long cache_rows, const int* block_table,
+                                                  int table_width, const int* positions, int rows, int page_size,
+                                                  int heads, int kv_heads, int head_dim, float scale, int window,
+                                                  int partition, int num_partitions, float* scratch,
+                                                  long long scratch_floats, cudaStream_t stream, const float* sinks,
+                                                  const void* gate, long long gate_stride) {
+  const AttentionExtras extras{sinks, (const bf16*)gate, gate_stride};
+  return decode_attention_tc_with(q, q_stride, out, k_pages, v_pages, cache_rows, block_table, table_width, positions,
+                                  rows, page_size, heads, kv_heads, head_dim, scale, window, partition, num_partitions,
+                                  scratch, scratch_floats, stream, extras);
+}
+
+// The same with scores that are capped (softcap > 0) and biased by distance (rel_bias [heads, rel_rows] 32-bit or
+// null), in 32-bit before the softmax, and with a gate of one column per head (gate_per_head).
+MIR_EXPORT int mir_decode_attention_tc_scored_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                                   const void* v_pages, long long cache_rows, const int* block_table,
+                                                   int table_width, const int* positions, int rows, int page_size,
+                                                   int heads, int kv_heads, int head_dim, float scale, int window,
+                                                   int partition, int num_partitions, float* scratch,
+                                                   long long scratch_floats, cudaStream_t stream, const float* sinks,
+                                                   const void* gate, long long gate_stride, int gate_per_head,
+                                                   float softcap, const float* rel_bias, int rel_rows) {
+  if (rel_bias != nullptr && rel_rows <= 0) { mir_set_error("decode_attention_tc: a bias by distance needs entries"); return MIR_BAD_ARGUMENT; }
+  const AttentionExtras extras{sinks, (const bf16*)gate, gate_stride, gate_per_head ? head_dim : 0, softcap, rel_bias,
+                               rel_rows, heads};
+  return decode_attention_tc_with(q, q_stride, out, k_pages, v_pages, cache_rows, block_table, table_width, positions,
+                                  rows, page_size, heads, kv_heads, head_dim, scale, window, partition, num_partitions,
+                                  scratch, scratch_floats, stream, extras);
 }
 
 MIR_EXPORT int mir_decode_attention_tc_bf16(const void* q, long long q_stride, void* out, const void* k_pages,

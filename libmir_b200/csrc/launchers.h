@@ -63,6 +63,24 @@ int mir_decode_attention_tc_extra_bf16(const void* q, long long q_stride, void* 
                                        int num_partitions, float* scratch, long long scratch_floats,
                                        cudaStream_t stream, const float* sinks, const void* gate,
                                        long long gate_stride);
+int mir_decode_merge_gated_bf16(const float* partial_o, const float* partial_ml, const int* positions, int rows,
+                                int heads, int head_dim, int window, int partition, int num_partitions, void* out,
+                                cudaStream_t stream, const float* sinks, const void* gate, long long gate_stride,
+                                int gate_head_width);
+int mir_decode_attention_scored_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                     const void* v_pages, const int* block_table, int table_width, const int* positions,
+                                     int rows, int page_size, int heads, int kv_heads, int head_dim, float scale,
+                                     int window, int partition, int num_partitions, float* scratch,
+                                     long long scratch_floats, cudaStream_t stream, const float* sinks, const void* gate,
+                                     long long gate_stride, int gate_per_head, float softcap, const float* rel_bias,
+                                     int rel_rows);
+int mir_decode_attention_tc_scored_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                        const void* v_pages, long long cache_rows, const int* block_table,
+                                        int table_width, const int* positions, int rows, int page_size, int heads,
+                                        int kv_heads, int head_dim, float scale, int window, int partition,
+                                        int num_partitions, float* scratch, long long scratch_floats,
+                                        cudaStream_t stream, const float* sinks, const void* gate, long long gate_stride,
+                                        int gate_per_head, float softcap, const float* rel_bias, int rel_rows);
 int mir_decode_attention_tc_takes(int head_dim, int page_size, int partition);
 int mir_decode_attention_tc_bf16(const void* q, long long q_stride, void* out, const void* k_pages, const void* v_pages,
                                  long long cache_rows, const int* block_table, int table_width, const int* positions,

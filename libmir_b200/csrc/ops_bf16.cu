@@ -166,6 +166,26 @@ MIR_EXPORT int mir_decode_attention_paged_extra_bf16(const void* q, long long q_
                                          scratch, scratch_floats, stream, 0, nullptr, sinks, gate, gate_stride);
 }
 
+// The same with capped and biased scores and a gate of one column per head, as mir_decode_attention_scored_bf16.
+MIR_EXPORT int mir_decode_attention_paged_scored_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                                      const void* v_pages, long long cache_rows, const int* block_table,
+                                                      int table_width, const int* positions, int rows, int page_size,
+                                                      int heads, int kv_heads, int head_dim, float scale, int window,
+                                                      int partition, int num_partitions, float* scratch,
+                                                      long long scratch_floats, cudaStream_t stream, const float* sinks,
+                                                      const void* gate, long long gate_stride, int gate_per_head,
+                                                      float softcap, const float* rel_bias, int rel_rows) {
+  if (g_decode_tensor_cores && cache_rows > 0 && mir_decode_attention_tc_takes(head_dim, page_size, partition))
+    return mir_decode_attention_tc_scored_bf16(q, q_stride, out, k_pages, v_pages, cache_rows, block_table, table_width,
+                                               positions, rows, page_size, heads, kv_heads, head_dim, scale, window,
+                                               partition, num_partitions, scratch, scratch_floats, stream, sinks, gate,
+                                               gate_stride, gate_per_head, softcap, rel_bias, rel_rows);
+  return mir_decode_attention_scored_bf16(q, q_stride, out, k_pages, v_pages, block_table, table_width, positions, rows,
+                                          page_size, heads, kv_heads, head_dim, scale, window, partition, num_partitions,
+                                          scratch, scratch_floats, stream, sinks, gate, gate_stride, gate_per_head, softcap,
+                                          rel_bias, rel_rows);
+}
+
 MIR_EXPORT int mir_decode_attention_paged_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
                                                const void* v_pages, long long cache_rows, const int* block_table,
                                                int table_width, const int* positions, int rows, int page_size,

@@ -115,6 +115,10 @@ _SIGNATURES = {
                                                  c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                                  c_float, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_float,
                                                  c_void_p, c_int],
+        "mir_decode_attention_paged_scored_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong,
+                                                   c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                                   c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p,
+                                                   c_void_p, c_longlong, c_int, c_float, c_void_p, c_int],
         "mir_prefill_attention_scored_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                               c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                               c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_float, c_void_p,
@@ -1337,8 +1341,8 @@ def decode_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor
     the window's as one run, and `numbering` (int32 [rows]) is scratch for the merge.  `sinks`, `gate`: as
     paged_attention_generic takes them (the kernel that writes a row's final result, the attention kernel or the
     merge of its partitions, adds the sink's term and applies the gate).  `gate_per_head`, `softcap`, `distance_bias`:
-    as paged_attention_generic takes them; with any of them the mma.sync kernel runs (the scores are capped and
-    biased in 32-bit before the softmax; partitions of decode_attention_kept_plan)."""
+    as paged_attention_generic takes them: the scores are capped and biased in 32-bit before the softmax, by the
+    tcgen05 kernel where it takes the sizes and the partition (decode_attention_plan), else by the mma.sync kernel."""
     _cuda(qkv, out, k_pages, v_pages, block_table, positions, scratch, sinks, gate, distance_bias)
     rows = out.shape[0]
     _check_extras("decode_attention", sinks, gate, out, heads, gate_per_head, distance_bias)
@@ -1354,8 +1358,8 @@ def decode_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor
              "decode_attention: the cache tensors must be contiguous [token rows, kv_heads, head_dim]")
     if gate_per_head or softcap or distance_bias is not None:
         _require(not (keep_first and window), "decode_attention: capped or biased scores do not go with kept first keys")
-        _check(lib, lib.mir_decode_attention_scored_bf16(
-            qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
+        _check(lib, lib.mir_decode_attention_paged_scored_bf16(
+            qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0],
             block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), rows, page_size, heads, kv_heads,
             head_dim, scale, int(window or 0), partition, num_partitions, _ptr(scratch),
             0 if scratch is None else scratch.numel(), _stream(), *gate_args, int(gate_per_head), float(softcap or 0.0),

@@ -248,14 +248,15 @@ class SoftmaxAttention(Mixer):
         scored = s.softcap is not None or self.distance_bias is not None or s.gate_per_head
         fast = self.env.dtype == torch.bfloat16 and s.head_dim in kernels.FAST_HEAD_DIMS and s.value_dim == s.head_dim
         if fast and scored and not kept:
-            # capped or biased scores, or a gate per head: single tokens run the mma.sync kernel split over the keys,
-            # portions run as tiles of queries on either tile kernel
+            # capped or biased scores, or a gate per head: single tokens split over the keys, portions as tiles of
+            # queries, each on the tcgen05 or the mma.sync kernel by size
             extras = dict(sinks=self.sinks, gate_per_head=s.gate_per_head, softcap=s.softcap,
                           distance_bias=self.distance_bias)
             singles = ctx.num_rows if ctx.decode_only else ctx.single_rows
             if singles:
                 longest = ctx.max_context if ctx.decode_only else ctx.single_context
-                partition, count, floats = kernels.decode_attention_kept_plan(singles, s.heads, s.head_dim, longest)
+                partition, count, floats = kernels.decode_attention_plan(singles, s.heads, s.kv_heads, s.head_dim,
+                                                                         cache.page_size, longest)
                 scratch = ctx.alloc((floats,), torch.float32) if floats else None
                 kernels.decode_attention(qkv[:singles], out[:singles], cache.k_pages, cache.v_pages,
                                          group.block_table[:singles], ctx.positions, cache.page_size, s.heads,

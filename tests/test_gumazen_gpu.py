@@ -325,13 +325,17 @@ def test_attention_with_capped_biased_scores_where_keys_at_the_edges_stand_out(d
     rows, gate = packed(singles)
     want = torch.cat([wants[r][a:b] for r, a, b in singles])
     positions = ints([n - 1 for n in lengths])
-    for keys_per_partition in (512, 64):
+    # (partitions of 512 and 128 keys run the tcgen05 kernel where it takes the sizes, of 64 keys the mma.sync kernel)
+    for keys_per_partition in (512, 128, 64):
         with kernels.option("decode_partition_keys", keys_per_partition):
             partition, count, floats = kernels.decode_attention_kept_plan(3, heads, dim, max(lengths))
             scratch = torch.empty(floats, dtype=torch.float32, device=device()) if floats else None
             out = torch.zeros(3, heads * vdim, dtype=dtype, device=device())
+            kernels.launch_counts(reset=True)
             kernels.decode_attention(rows, out, k_pool, v_pool, table, positions, page, heads, kv_heads, dim, scale, window,
                                      partition, count, scratch, gate=gate, **extras)
+            on_tcgen05 = dim == 128 and page % 8 == 0 and keys_per_partition % 128 == 0
+            assert (kernels.launch_counts().get("decode_attention_tc", 0) == 1) == on_tcgen05, kernels.launch_counts()
         close(out, want, tol, f"single tokens, partitions of {keys_per_partition} keys")
 
 
@@ -599,7 +603,7 @@ def test_the_windows_edge_and_the_buckets_show_in_the_logits(tmp_path, dim, page
 
 def test_the_tensor_core_kernels_run_the_designs_attention_in_bfloat16(tmp_path):
     """Heads of 64 and 128 channels: prompts and single tokens of all three kinds of attention run the tile kernels
-    (prompts of heads with 128 channels on tcgen05, the others on mma.sync), not the reference kernel."""
+    (heads of 128 channels on tcgen05, of 64 on mma.sync), not the reference kernel."""
     from libmir_b200 import kernels
     for name in ("C", "D"):
         config = ALL[name]
@@ -610,8 +614,9 @@ def test_the_tensor_core_kernels_run_the_designs_attention_in_bfloat16(tmp_path)
         feed(model, "x", ids, [70, 1])
         counts = kernels.launch_counts()
         assert counts.get("paged_attention_generic", 0) == 0, counts
-        tiles = "prefill_attention_tc" if name == "D" else "prefill_attention"      # heads of 128 channels: tcgen05
-        assert counts.get(tiles, 0) > 0 and counts.get("decode_attention", 0) > 0, counts
+        tiles, split = ("prefill_attention_tc", "decode_attention_tc") if name == "D" else \
+            ("prefill_attention", "decode_attention")                              # heads of 128 channels: tcgen05
+        assert counts.get(tiles, 0) > 0 and counts.get(split, 0) > 0, counts
         assert counts.get("qk_prepare", 0) > 0 and counts.get("layer_norm", 0) > 0
 
 
