@@ -339,23 +339,6 @@ def test_attention_with_capped_biased_scores_where_keys_at_the_edges_stand_out(d
         close(out, want, tol, f"single tokens, partitions of {keys_per_partition} keys")
 
 
-def test_the_bias_table_is_spread_by_the_bucket_rule():
-    """What the attention part hands to the kernels: one entry per distance and head [heads, distances], ending where the last bucket or the window's
-    end is reached; for constants whose buckets fall on exact powers too."""
-    from libmir_b200.config.spec import DistanceBiasSpec, SoftmaxAttentionSpec
-    from libmir_b200.parts import BuildEnv, SoftmaxAttention
-    for rows, farthest, window in ((24, 150.0, 80), (12, 40.0, 20), (2, 5.0, 3), (8, 64.0, None), (5, 3.0, 200), (16, 70.0, 1)):
-        spec = SoftmaxAttentionSpec(hidden_size=16, heads=3, kv_heads=1, head_dim=8, window=window,
-                                    distance_bias=DistanceBiasSpec(rows=rows, farthest=farthest))
-        part = SoftmaxAttention(spec, BuildEnv(torch.float32, torch.device("cpu")))
-        table = torch.arange(rows * 3, dtype=torch.float32).view(rows, 3)
-        got = part.bias_by_distance(table).t()
-        for n in range(got.shape[0]):
-            assert torch.equal(got[n], table[plain.distance_bucket(n, rows, farthest)])
-        last = got.shape[0] - 1
-        assert (window is not None and last == window - 1) or plain.distance_bucket(last, rows, farthest) == rows - 1
-
-
 # ------------------------------------------------------------------------------ experts
 @pytest.mark.parametrize("experts,identity,top,groups,keep", [(10, 6, 5, 4, 3), (6, 2, 3, 4, 2), (1, 0, 1, 1, 1), (3, 3, 3, 6, 6),
                                                               (4, 4, 2, 2, 1), (5, 1, 2, 3, 2), (7, 0, 7, 1, 1)])
