@@ -233,6 +233,16 @@ __global__ void streams_write_norm_kernel(float* __restrict__ x, const float* __
       sum += mixed[v];
     }
   }
+  if (weight == nullptr) {                         // no norm: the mix itself (the sum of the streams at the model's end)
+    T* dst = out + token * width;
+    for (int c = threadIdx.x * V; c < width; c += blockDim.x * V) {
+      float values[V];
+#pragma unroll
+      for (int v = 0; v < V; ++v) values[v] = row_values[c + v];    // (this thread's own columns)
+      store_columns<T, V>(dst + c, values);
+    }
+    return;
+  }
   norm_row<T, V>(row_values, sum, scratch, weight, bias, out + token * width, width, eps);
 }
 
@@ -316,7 +326,7 @@ MIR_EXPORT int mir_streams_write(float* x, const float* y, const float* mix, con
 }
 
 // mir_streams_write, and out [tokens, width] = the layer norm (weight, bias or null, eps) of the mix sum_s read[s] x_s of
-// the streams as they are after the update; out in bfloat16 or 32-bit.
+// the streams as they are after the update; out in bfloat16 or 32-bit.  weight null: out is the mix itself.
 MIR_EXPORT int mir_streams_write_norm(int bf16, float* x, const float* y, const float* mix, const float* write,
                                       const float* read, const float* weight, const float* bias, void* out, int tokens,
                                       int streams, int width, float eps, cudaStream_t stream) {

@@ -1039,24 +1039,26 @@ def streams_write(streams: torch.Tensor, branch: torch.Tensor, mix: torch.Tensor
 
 
 def streams_write_norm(streams: torch.Tensor, branch: torch.Tensor, mix: torch.Tensor, write: torch.Tensor,
-                       read: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float,
+                       read: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor], eps: float,
                        out: torch.Tensor) -> None:
     """streams_write, and in the same pass over a token out = layer_norm(sum_s read[s] x_s) of the streams as the update
     leaves them (what layer_norm with `read` would give for them): the next sublayer's input without a second trip of
-    the streams through memory."""
+    the streams through memory.  Without `weight`, out is the mix itself (with `read` of ones: the sum of the streams
+    that the model ends with)."""
     _cuda(streams, branch, mix, write, read, weight, bias, out)
     tokens, count, width = streams.shape
     _require(streams.dtype == torch.float32 and streams.is_contiguous() and branch.dtype == torch.float32
              and branch.is_contiguous() and branch.shape == (tokens, width) and mix.dtype == torch.float32
              and mix.is_contiguous() and mix.shape == (count, count) and write.dtype == torch.float32
              and write.numel() == count and read.dtype == torch.float32 and read.numel() == count
-             and weight.dtype == torch.float32 and weight.numel() == width
-             and (bias is None or (bias.dtype == torch.float32 and bias.numel() == width)) and out.is_contiguous()
+             and (weight is None or (weight.dtype == torch.float32 and weight.numel() == width))
+             and (bias is None or (weight is not None and bias.dtype == torch.float32 and bias.numel() == width))
+             and out.is_contiguous()
              and out.shape == (tokens, width) and out.dtype in (torch.bfloat16, torch.float32),
              "streams_write_norm: bad arguments")
     lib = library("core")
     _check(lib, lib.mir_streams_write_norm(_is_bf16(out), streams.data_ptr(), branch.data_ptr(), mix.data_ptr(),
-                                           write.data_ptr(), read.data_ptr(), weight.data_ptr(), _ptr(bias), out.data_ptr(),
+                                           write.data_ptr(), read.data_ptr(), _ptr(weight), _ptr(bias), out.data_ptr(),
                                            tokens, count, width, eps, _stream()))
 
 

@@ -219,11 +219,13 @@ class DecoderModel:
         for index, entry in enumerate(spec.schedule):
             # who reads the streams first in the next block: this block's last update norms their mix on the way out
             following = self.blocks[spec.schedule[index + 1].layer] if index + 1 < len(spec.schedule) else None
-            ctx.streams_reader_after_block = following.first_reader() if following is not None else None
+            ctx.streams_reader_after_block = following.first_reader() if following is not None else "sum"
             self.blocks[entry.layer].forward(ctx, ctx.cache_view(index), streams)
             if self.after_entry is not None:
                 self.after_entry(index, streams)
-        ctx.streams_reader_after_block = ctx.normed_streams = None
+        total, ctx.streams_reader_after_block, ctx.normed_streams = ctx.normed_streams, None, None
+        if total is not None and total.dtype == torch.float32 and total.shape == embedded.shape:
+            return total                     # the last update left the streams' sum
         kernels.streams_sum(streams, embedded)
         return embedded
 

@@ -243,7 +243,7 @@ class StreamMix(Part):
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
-        self.read = self.write = self.mix = None
+        self.read = self.write = self.mix = self.ones = None
 
     def parameters(self):
         from ..config.spec import ParamSpec
@@ -254,6 +254,7 @@ class StreamMix(Part):
 
     def bind(self, tensors):
         self.read, self.write, self.mix = (tensors[name].contiguous() for name in ("in", "out", "mix"))
+        self.ones = torch.ones_like(self.read)          # the factors of a reader that takes the streams' plain sum
 
     def weight_bytes(self):
         return sum(t.numel() * 4 for t in (self.read, self.write, self.mix))
@@ -306,11 +307,15 @@ class StreamsBlock(Block):
 
     def _write(self, ctx, residual, result, streams, reader):
         """The streams take a sublayer's result; with a reader (norm, mixing tensors) the same kernel leaves the normed
-        mix of the new streams that this reader starts from, which is returned."""
+        mix of the new streams that this reader starts from, which is returned; the reader "sum" gets their 32-bit sum."""
         from .. import kernels
         if reader is None:
             kernels.streams_write(residual, result, streams.mix, streams.write)
             return None
+        if reader == "sum":                  # the model's last update: the streams' sum, 32-bit, on the way out
+            total = ctx.alloc((residual.shape[0], residual.shape[2]), torch.float32)
+            kernels.streams_write_norm(residual, result, streams.mix, streams.write, streams.ones, None, None, 0.0, total)
+            return total
         norm, following = reader
         out = ctx.alloc((residual.shape[0], residual.shape[2]), self.env.dtype)
         kernels.streams_write_norm(residual, result, streams.mix, streams.write, following.read, norm.weight, norm.bias,

@@ -130,6 +130,12 @@ def test_the_update_of_the_streams_also_norms_the_next_readers_mix(dtype, tol, c
     twice = on_device(start)
     kernels.streams_write(twice, on_device(branch), on_device(mix), on_device(write))
     assert torch.equal(twice, streams), "the same streams as the update alone leaves"
+    # without a norm: the mix itself; with factors of one, the sum that streams_sum gives, bit for bit
+    again, total, summed = on_device(start), torch.empty(tokens, width, device=device()), torch.empty(tokens, width, device=device())
+    kernels.streams_write_norm(again, on_device(branch), on_device(mix), on_device(write), torch.ones(count, device=device()),
+                               None, None, 0.0, total)
+    kernels.streams_sum(again, summed)
+    assert torch.equal(again, streams) and torch.equal(total, summed)
 
 
 # ------------------------------------------------------------------------------ q/k treatment
