@@ -322,7 +322,10 @@ moe_grouped_kernel(const T* __restrict__ x, long long ldx, const int* __restrict
 // + shared_rows[t] without a gate), slots in their own order.  A slot whose expert is an identity expert (ids[pair] >=
 // real_experts) has no row: it adds weight * the token's own input (identity_rows, in the activations' type).
 // overwrite: the sum replaces residual[t] instead of being added to it.
-template <typename T>
+// A thread takes V neighbouring columns of one token (V = 4 where rows and pointers allow 16-byte accesses), a CTA a
+// run of columns (blockIdx.y): few tokens still fill the GPU.  A column's sum runs over the slots in ascending order,
+// then the shared expert, whatever V is.
+template <typename T, int V>
 __global__ void moe_combine_kernel(float* __restrict__ residual, const float* __restrict__ pair_rows,
                                    const float* __restrict__ weights, const float* __restrict__ shared_rows,
                                    const float* __restrict__ shared_gate, int width, int top, int overwrite,
@@ -331,19 +334,35 @@ __global__ void moe_combine_kernel(float* __restrict__ residual, const float* __
   grid_launch_dependents();
   grid_dependency_wait();
   const int token = blockIdx.x;
-  const float gate = shared_rows != nullptr ? (shared_gate != nullptr ? shared_gate[token] : 1.0f) : 0.0f;
-  for (int c = threadIdx.x; c < width; c += blockDim.x) {
-    float total = 0.0f;
-    for (int s = 0; s < top; ++s) {
-      const size_t pair = (size_t)token * top + s;
-      const float row = (ids != nullptr && ids[pair] >= real_experts)
-                            ? to_float(identity_rows[(size_t)token * identity_stride + c])
-                            : pair_rows[pair * width + c];
-      total = fmaf(weights[pair], row, total);
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+  if (c >= width) return;
+  float total[V];
+#pragma unroll
+  for (int v = 0; v < V; ++v) total[v] = 0.0f;
+  for (int s = 0; s < top; ++s) {
+    const size_t pair = (size_t)token * top + s;
+    const float weight = __ldg(weights + pair);
+    alignas(16) float row[V];
+    if (ids != nullptr && __ldg(ids + pair) >= real_experts) {
+      const T* src = identity_rows + (size_t)token * identity_stride + c;
+#pragma unroll
+      for (int v = 0; v < V; ++v) row[v] = to_float(src[v]);
+    } else if (V == 4) {
+      *reinterpret_cast<float4*>(row) = *reinterpret_cast<const float4*>(pair_rows + pair * width + c);
+    } else {
+      row[0] = pair_rows[pair * width + c];
     }
-    if (shared_rows != nullptr) total = fmaf(gate, shared_rows[(size_t)token * width + c], total);
-    residual[(size_t)token * width + c] = overwrite ? total : residual[(size_t)token * width + c] + total;
+#pragma unroll
+    for (int v = 0; v < V; ++v) total[v] = fmaf(weight, row[v], total[v]);
   }
+  const size_t at = (size_t)token * width + c;
+  if (shared_rows != nullptr) {
+    const float gate = shared_gate != nullptr ? shared_gate[token] : 1.0f;
+#pragma unroll
+    for (int v = 0; v < V; ++v) total[v] = fmaf(gate, shared_rows[at + v], total[v]);
+  }
+#pragma unroll
+  for (int v = 0; v < V; ++v) residual[at + v] = overwrite ? total[v] : residual[at + v] + total[v];
 }
 
 template <typename T, typename TO, bool GATED>
@@ -469,12 +488,19 @@ MIR_EXPORT int mir_moe_combine(float* residual, const float* pair_rows, const fl
     mir_set_error("moe_combine: identity experts need the tokens' input rows");
     return MIR_BAD_ARGUMENT;
   }
-  const int threads = width >= 1024 ? 256 : 128;
-  if (bf16)
-    return mir_launch("moe_combine", moe_combine_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, 0, residual,
-                      pair_rows, weights, shared_rows, shared_gate, width, top, overwrite, ids, real_experts,
-                      (const __nv_bfloat16*)identity_rows, identity_stride);
-  return mir_launch("moe_combine", moe_combine_kernel<float>, dim3(tokens), dim3(threads), 0, stream, 0, residual, pair_rows,
-                    weights, shared_rows, shared_gate, width, top, overwrite, ids, real_experts,
-                    (const float*)identity_rows, identity_stride);
+  const bool wide = width % 4 == 0 && ((uintptr_t)pair_rows & 15) == 0;
+  const int per_thread = wide ? 4 : 1;
+  const int threads = width >= 1024 * per_thread ? 256 : 128;
+  const dim3 grid(tokens, (width + threads * per_thread - 1) / (threads * per_thread));
+#define MIR_COMBINE(T, V)                                                                                             \
+  return mir_launch("moe_combine", moe_combine_kernel<T, V>, grid, dim3(threads), 0, stream, 0, residual, pair_rows,   \
+                    weights, shared_rows, shared_gate, width, top, overwrite, ids, real_experts, (const T*)identity_rows, \
+                    identity_stride)
+  if (bf16) {
+    if (wide) MIR_COMBINE(__nv_bfloat16, 4);
+    MIR_COMBINE(__nv_bfloat16, 1);
+  }
+  if (wide) MIR_COMBINE(float, 4);
+  MIR_COMBINE(float, 1);
+#undef MIR_COMBINE
 }
